@@ -19,9 +19,9 @@ N_NEW=5 timeout 900 ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dr
 timeout 600 ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --clock-control none \
   -k regex:'resample_|pad_fill' -s 18 -c 36 --csv --log-file gpurun_out/${T}_frontend_launches.csv \
   python tools/gpu_frontend_prof.py >> gpurun_out/${T}_prof.log 2>&1
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:attn3_fwd -s 2 -c 1 -f -o gpurun_out/${T}_attn3_dec \
+timeout 900 ncu --set full --clock-control none -k regex:attn3_fwd -s 2 -c 1 -f -o gpurun_out/${T}_attn3_dec \
   python tools/gpu_check_attn.py --case dec_4796_c --variant 80 --time >> gpurun_out/${T}_prof.log 2>&1
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:attn3_fwd -s 2 -c 1 -f -o gpurun_out/${T}_attn3_vit \
+timeout 900 ncu --set full --clock-control none -k regex:attn3_fwd -s 2 -c 1 -f -o gpurun_out/${T}_attn3_vit \
   python tools/gpu_check_attn.py --case vit_28 --variant 80 --time >> gpurun_out/${T}_prof.log 2>&1
 timeout 900 ncu --set full --clock-control none -k regex:gemv3_kernel -s 262 -c 5 -f -o gpurun_out/${T}_gemv \
   python tools/gpu_decode_prof.py >> gpurun_out/${T}_prof.log 2>&1

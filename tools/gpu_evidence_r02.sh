@@ -16,7 +16,7 @@ echo "launches per step: $N"
 KR='regex:gemm_|attn|norm_kernel|rmsnorm|rope|merge_|im2col|pixel_shuffle|row_stats'
 timeout 900 ncu --metrics gpu__time_duration.sum --clock-control none -k "$KR" -s $N -c $N --csv \
     --log-file gpurun_out/${T}_launches.csv python bench.py --quick --steps 1 --warmup 1 > gpurun_out/${T}_prof.log 2>&1
-NCU="ncu --set full --clock-control none --import-source on"
+NCU="ncu --set full --clock-control none"
 timeout 600 $NCU -k regex:gemm_bf16_kernel -s 2 -c 1 -f -o gpurun_out/${T}_gemm_gateup python tools/gpu_check_gemm.py --pair --time --case d_gateup >> gpurun_out/${T}_prof.log 2>&1
 timeout 600 $NCU -k regex:gemm_bf16_res_kernel -s 2 -c 1 -f -o gpurun_out/${T}_gemm_d_down python tools/gpu_check_gemm.py --pair --time --case d_down >> gpurun_out/${T}_prof.log 2>&1
 timeout 600 $NCU -k regex:gemm_bf16_res_kernel -s 2 -c 1 -f -o gpurun_out/${T}_gemm_v_out python tools/gpu_check_gemm.py --pair --time --case v_out >> gpurun_out/${T}_prof.log 2>&1
@@ -31,5 +31,5 @@ timeout 900 python bench.py --workload cfg5 --steps 3 > gpurun_out/${T}_bench_cf
 for r in gemm_gateup gemm_d_down gemm_v_out gemm_v_fc2 gemm_chain attn3_dec attn3_vit attn5_vit; do
   python tools/ncu_summary.py gpurun_out/${T}_$r.ncu-rep > gpurun_out/${T}_$r.txt 2>/dev/null
 done
-rm -f gpurun_out/${T}_gemm_gateup.ncu-rep gpurun_out/${T}_gemm_d_down.ncu-rep gpurun_out/${T}_gemm_chain.ncu-rep gpurun_out/${T}_gemm_v_fc2.ncu-rep gpurun_out/${T}_attn3_vit.ncu-rep   # summaries travel; keep the reports with source pages
+rm -f gpurun_out/${T}_gemm_gateup.ncu-rep gpurun_out/${T}_gemm_d_down.ncu-rep gpurun_out/${T}_gemm_chain.ncu-rep gpurun_out/${T}_gemm_v_fc2.ncu-rep gpurun_out/${T}_attn3_vit.ncu-rep   # summaries travel
 ls -la gpurun_out/${T}_* | awk '{print $5, $9}'

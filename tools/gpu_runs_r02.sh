@@ -61,11 +61,11 @@ r02a() {
 }
 
 r02b() {
-  # Round 2, second GPU call: SFT suite after the fixes + ncu --set full captures (with source) of the kernels VERDICT r1 names:
+  # Round 2, second GPU call: SFT suite after the fixes + ncu --set full captures of the kernels VERDICT r1 names:
   # the short-K ViT GEMMs with a residual epilogue and the ViT attention.
   T=${TAG:-r02b}
   run train_tests python -m pytest tests/test_zz_gpu_train.py -q -rA --tb=short
-  NCU="ncu --set full --clock-control none --import-source on"
+  NCU="ncu --set full --clock-control none"
   for c in v_out v_fc2 v_patch v_qkv; do
     TMO=300 run ncu_gemm_$c $NCU -k regex:gemm_bf16 -s 1 -c 1 -o gpurun_out/${T}_gemm_$c -f python tools/gpu_check_gemm.py --pair --case $c
   done
@@ -84,7 +84,7 @@ r02c() {
   run bench_cfg5 python bench.py --workload cfg5 --steps 3
   run bench_cfg5_frozen python bench.py --workload cfg5 --steps 3 --sft-freeze-vit
   TMO=1500 run fullsize python -m pytest tests/test_gpu_fullsize.py tests/test_gpu_model.py -q -s -k "full_depth" 
-  NCU="ncu --set full --clock-control none --import-source on"
+  NCU="ncu --set full --clock-control none"
   for c in v_out v_fc2 v_patch d_o; do
     TMO=300 run ncu_gemm_$c $NCU -k regex:gemm_bf16 -s 2 -c 1 -o gpurun_out/${T}_gemm_$c -f python tools/gpu_check_gemm.py --pair --time --case $c
   done
@@ -140,7 +140,7 @@ r02h() {
 
 r02i() {
   # Round 2: stream-K with the data-parallel waves first (START / whole / END pieces at the end), every switch combination per shape,
-  # whole-step A/B, ncu source-level capture of the LayerNorm-consuming fc1 GEMM inside a real step.
+  # whole-step A/B, ncu capture of the LayerNorm-consuming fc1 GEMM inside a real step.
   T=${TAG:-r02i}
   TMO=900 run ops python -m pytest tests/test_gpu_ops.py -x -q -k "gemm"
   SH="--case d_o --case d_down --case d_qkv --case dec_o --case dec_down --case dec_qkv --case p_1 --case v_fc2 --case v_out"
@@ -148,7 +148,7 @@ r02i() {
     TAIL=3000 run gemm_sk${sk}_tma${tm} python tools/gpu_check_gemm.py --pair --time --streamk $sk --tma-res $tm $SH
   done; done
   TMO=900 run ab python tools/gpu_ab_prefill.py sk=0 sk=1
-  NCU="ncu --set full --clock-control none --import-source on"
+  NCU="ncu --set full --clock-control none"
   TMO=400 run ncu_fc1 $NCU -k regex:gemm_bf16_kernel --launch-skip 122 --launch-count 1 -o gpurun_out/${T}_gemm_fc1_ln -f python bench.py --quick --steps 1 --warmup 1
   ls -la gpurun_out/${T}_* | awk '{print $5, $9}'
 }
