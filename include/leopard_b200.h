@@ -576,6 +576,87 @@ int lp_parity_add(float* y, long long ldy, const float* x, long long ldx, int M,
 int lp_parity_rope(float* x, long long ld, int S, int n_heads, int head_dim, const float* cs, const float* sn, void* stream);
 int lp_parity_softmax(float* scores, long long ld, int Tq, int Tk, float scale, int causal, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * 32-BIT RESIDUAL-STREAM MODELS (leopard_b200/seqlm.py): decoder-only language models whose residual sum, norms, routers, attention
+ * scores and recurrent state are kept in fp32, served from a paged latent cache and a slot pool of recurrent states.  The
+ * mechanisms are separate entry points with their constants as arguments, so that a model description (a list of layers) composes
+ * them: csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_moe.cu.
+ * ------------------------------------------------------------------------------------------------------------------ */
+enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2 };
+enum lp_rot_layout { LP_ROT_HALF = 0, LP_ROT_INTERLEAVED = 1 };
+#define LP_RETENTION_CHUNK 32
+
+/* C[M, N'] = epi(A[M, K] W[N, K]^T), `batch` problems `*_batch` elements apart.  A: fp32 (a_fp32) or bf16; W: bf16; C: fp32 (c_fp32) or
+ * bf16.  epi XIELU: a z^2 + z/2 (z > 0), b (exp(z) - 1 - z) + z/2 (z <= 0) with a = epi_a, b = epi_b.  epi SILU_GATE: W = [gate rows;
+ * up rows], N' = N / 2, C = silu(gate) * up.  fp32 FMA accumulation in K order. */
+typedef struct lp_linear_desc {
+  const void* A; long long lda; long long a_batch; int a_fp32;
+  const void* W; long long ldw; long long w_batch;
+  void* C; long long ldc; long long c_batch; int c_fp32;
+  int M, N, K, batch;
+  int epi; float epi_a, epi_b;
+} lp_linear_desc;
+int lp_linear(const lp_linear_desc* desc, void* stream);
+/* row tiles of lp_linear_tile_rows() rows, each multiplied by the weight of group tile_group[tile] (w_batch elements apart; < 0: the
+ * tile is skipped); a_rows[row] (optional) = the A row to read for that row of the sorted space (< 0: zeros). */
+int lp_linear_grouped(const lp_linear_desc* desc, const int* tile_group, int n_tiles, const int* a_rows, void* stream);
+int lp_linear_tile_rows(void);
+
+int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float* out, long long ldo, int D, void* stream);
+/* y = x / sqrt(mean(x^2) + eps) * gain_scalar (* gain_vec[c]); written to `out` (fp32 or bf16) or added to `accum` (fp32) */
+int lp_rmsnorm_f32(const float* x, long long ldx, int M, int D, float gain_scalar, const float* gain_vec, float eps, void* out,
+                   long long ldo, int out_fp32, float* accum, long long ld_accum, void* stream);
+/* standalone activation for products that ran on lp_gemm_bf16: mode XIELU (N columns) or SILU_GATE (in has 2N columns: gate | up) */
+int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode, float a,
+               float b, void* stream);
+
+/* Retention over a packed batch.  qkvg fp32 [rows, ld] holds q | k (heads x dim) and v | g (heads x vdim) at the given column offsets.
+ * state fp32 [slots][heads][dim][vdim] (slot_stride elements per slot).  out [rows, heads * vdim] fp32 or bf16. */
+typedef struct lp_retention_desc {
+  const float* qkvg; long long ld; int q_off, k_off, v_off, g_off;
+  int heads, dim, vdim;
+  const float* decay;                       /* [heads] */
+  const float* inv_freq; int rot_dims; int rot_layout; float rot_mscale;
+  float k_scale, eps;
+  float* state; long long slot_stride;
+  void* out; long long ldo; int out_fp32;
+} lp_retention_desc;
+size_t lp_retention_workspace_bytes(int n_chunks, int heads, int dim, int vdim);
+/* Request s owns packed rows [seq_row0[s], seq_row0[s+1]), its first row is position seq_pos0[s], its state lives in slot seq_slot[s];
+ * chunks (at most LP_RETENTION_CHUNK rows, never across requests) are listed request by request: chunks [seq_chunk0[s],
+ * seq_chunk0[s+1]) belong to request s.  All index arrays are device int32. */
+int lp_retention_prefill(const lp_retention_desc* desc, int n_seqs, int n_chunks, const int* seq_row0, const int* seq_pos0,
+                         const int* seq_slot, const int* seq_chunk0, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
+                         void* workspace, size_t workspace_bytes, void* stream);
+/* one row per request: row seq_row0[s] at position seq_pos0[s] */
+int lp_retention_decode(const lp_retention_desc* desc, int n_seqs, const int* seq_row0, const int* seq_pos0, const int* seq_slot,
+                        void* stream);
+
+/* Latent attention over a paged cache of rows [c (kv_rank) | rotated shared key (rot_dim)] fp32; page_table int32 [requests, max_pages]. */
+typedef struct lp_latent_desc {
+  float* q; long long ldq;                  /* [rows, heads * (dim + rot_dim)]: per head [unrotated | rotated] */
+  const float* dkv; long long lddkv;        /* [rows, kv_rank + rot_dim] (lp_latent_prep only) */
+  int heads, dim, rot_dim, kv_rank;
+  const float* c_gain; float eps;           /* RMS norm of the latent: vector gain */
+  const float* inv_freq; int rot_dims; int rot_layout; float rot_mscale;
+  float* cache; int page_size;
+  const int* page_table; int max_pages;
+  int window; float scale;
+} lp_latent_desc;
+int lp_latent_prep(const lp_latent_desc* desc, int R, const int* row_seq, const int* row_pos, void* stream);
+/* q_abs fp32 [rows, heads * kv_rank] = per-head W_uk^T q_unrotated; out [rows, heads * kv_rank] = softmax-weighted sum of cached c */
+int lp_latent_attend(const lp_latent_desc* desc, int R, const int* row_seq, const int* row_pos, const float* q_abs, long long ldqa,
+                     void* out, long long ldo, int out_fp32, void* stream);
+
+int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
+                 const float* correction, int n_groups, int keep_groups, int top, const void* w_gate, int* idx_out, float* w_out,
+                 float* gate_out, void* stream);
+int lp_moe_max_tiles(int n_pairs, int E, int tile_rows);
+int lp_moe_align(const int* idx, int n_pairs, int top, int E, int tile_rows, int max_tiles, int* tile_group, int* sorted_token,
+                 int* pair_row, void* stream);
+int lp_moe_combine(const float* y, long long ldy, const int* pair_row, const float* w, int top, const float* shared, long long lds,
+                   const float* gate, float* out, long long ldo, int T, int D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -77,6 +77,32 @@ class ProfileRecord(C.Structure):
 
 _P = C.POINTER
 
+EPI_NONE, EPI_XIELU, EPI_SILU_GATE = 0, 1, 2
+ROT_HALF, ROT_INTERLEAVED = 0, 1
+RETENTION_CHUNK = 32
+
+
+class LinearDesc(C.Structure):
+    """lp_linear_desc (include/leopard_b200.h)."""
+    _fields_ = [("A", _vp), ("lda", _ll), ("a_batch", _ll), ("a_fp32", _i), ("W", _vp), ("ldw", _ll), ("w_batch", _ll), ("C", _vp),
+                ("ldc", _ll), ("c_batch", _ll), ("c_fp32", _i), ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("epi", _i),
+                ("epi_a", _f), ("epi_b", _f)]
+
+
+class RetentionDesc(C.Structure):
+    """lp_retention_desc (include/leopard_b200.h)."""
+    _fields_ = [("qkvg", _vp), ("ld", _ll), ("q_off", _i), ("k_off", _i), ("v_off", _i), ("g_off", _i), ("heads", _i), ("dim", _i),
+                ("vdim", _i), ("decay", _vp), ("inv_freq", _vp), ("rot_dims", _i), ("rot_layout", _i), ("rot_mscale", _f),
+                ("k_scale", _f), ("eps", _f), ("state", _vp), ("slot_stride", _ll), ("out", _vp), ("ldo", _ll), ("out_fp32", _i)]
+
+
+class LatentDesc(C.Structure):
+    """lp_latent_desc (include/leopard_b200.h)."""
+    _fields_ = [("q", _vp), ("ldq", _ll), ("dkv", _vp), ("lddkv", _ll), ("heads", _i), ("dim", _i), ("rot_dim", _i), ("kv_rank", _i),
+                ("c_gain", _vp), ("eps", _f), ("inv_freq", _vp), ("rot_dims", _i), ("rot_layout", _i), ("rot_mscale", _f),
+                ("cache", _vp), ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("window", _i), ("scale", _f)]
+
+
 # name -> (restype, argtypes); must list EVERY symbol include/leopard_b200.h declares (tests/test_abi.py checks)
 _SIGS = {
     "lp_last_error": (C.c_char_p, []),
@@ -162,6 +188,21 @@ _SIGS = {
     "lp_grad_norm_finish": (_i, [_vp, _f, _vp, _vp]),
     "lp_adamw_step": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _i, _vp, _vp]),
     "lp_launch_count": (_ll, []),
+    "lp_linear": (_i, [C.POINTER(LinearDesc), _vp]),
+    "lp_linear_grouped": (_i, [C.POINTER(LinearDesc), _vp, _i, _vp, _vp]),
+    "lp_linear_tile_rows": (_i, []),
+    "lp_embed_rows_f32": (_i, [_vp, _i, _vp, _ll, _i, _vp, _ll, _i, _vp]),
+    "lp_rmsnorm_f32": (_i, [_vp, _ll, _i, _i, _f, _vp, _f, _vp, _ll, _i, _vp, _ll, _vp]),
+    "lp_glu_f32": (_i, [_vp, _ll, _i, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp]),
+    "lp_retention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "lp_retention_prefill": (_i, [C.POINTER(RetentionDesc), _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "lp_retention_decode": (_i, [C.POINTER(RetentionDesc), _i, _vp, _vp, _vp, _vp]),
+    "lp_latent_prep": (_i, [C.POINTER(LatentDesc), _i, _vp, _vp, _vp]),
+    "lp_latent_attend": (_i, [C.POINTER(LatentDesc), _i, _vp, _vp, _vp, _ll, _vp, _ll, _i, _vp]),
+    "lp_moe_route": (_i, [_vp, _ll, _i, _i, _i, _vp, _ll, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "lp_moe_max_tiles": (_i, [_i, _i, _i]),
+    "lp_moe_align": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "lp_moe_combine": (_i, [_vp, _ll, _vp, _vp, _i, _vp, _ll, _vp, _vp, _ll, _i, _i, _vp]),
     "lp_profile_enable": (_i, [_i]),
     "lp_profile_read": (_i, [_vp, _i]),
 }
@@ -197,6 +238,56 @@ def lib():
             L.lp_set_prefill_pdl(int(os.environ["LEOPARD_PREFILL_PDL"]))
         _lib = L
     return _lib
+
+
+# ---- the 32-bit residual-stream entry points (csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_moe.cu) -----------------------------------
+# They need none of the tcgen05 translation units, so a model that uses only them can run from a library of its own that compiles in
+# seconds (build.build_native("stream32")); the full library contains the same symbols and is preferred when it is already built.
+STREAM32_LIB_PATH = PKG / "lib" / "libleopard_stream32.so"
+STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_linear", "lp_linear_grouped", "lp_linear_tile_rows",
+                    "lp_embed_rows_f32", "lp_rmsnorm_f32", "lp_glu_f32", "lp_retention_workspace_bytes", "lp_retention_prefill",
+                    "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
+                    "lp_moe_combine")
+_stream32 = None
+
+
+def bind_stream32(L):
+    """Set the signatures of the 32-bit residual-stream entry points on a loaded library (the native one, or the CPU-emulated build
+    of the same sources that the tests make)."""
+    for name in STREAM32_SYMBOLS:
+        try:
+            fn = getattr(L, name)
+        except AttributeError as e:
+            raise NativeError(f"the library does not export {name}: rebuild it") from e
+        fn.restype, fn.argtypes = _SIGS[name]
+    return L
+
+
+def stream32_lib(build: bool = True):
+    """The native library with the 32-bit residual-stream entry points: the full library when it is built and current, else the small
+    one (built on first use when `build`)."""
+    global _stream32
+    if _stream32 is None:
+        from . import build as _build
+        if _lib is not None or _build.is_current():
+            _stream32 = lib()
+        else:
+            if build:
+                _build.build_native(component="stream32")
+            if not STREAM32_LIB_PATH.exists():
+                raise NativeError(f"{STREAM32_LIB_PATH} not found: build it with `python -m leopard_b200.build stream32`")
+            try:
+                _stream32 = bind_stream32(C.CDLL(str(STREAM32_LIB_PATH)))
+            except OSError as e:  # pragma: no cover
+                raise NativeError(f"cannot load {STREAM32_LIB_PATH}: {e}") from e
+    return _stream32
+
+
+def check_on(L, rc: int, what: str):
+    """`check` for a call made on library L (its own error text)."""
+    if rc != 0:
+        msg = L.lp_last_error()
+        raise NativeError(f"{what} failed (status {rc}): {msg.decode() if msg else '?'}")
 
 
 _streamk_ws = None   # the device buffer handed to lp_gemm_set_streamk_workspace (kept alive here)

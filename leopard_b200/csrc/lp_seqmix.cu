@@ -1,0 +1,476 @@
+// leopard_b200 — sequence mixers with 32-bit scores and state, over packed batches of requests (prefill rows or one row per request).
+//
+//   Rotary positions     angle = position * inv_freq[i] in fp32, accurate sincosf; two pairings: LP_ROT_HALF (i with i + dims/2) and
+//                        LP_ROT_INTERLEAVED (2i with 2i + 1); both cos and sin carry a magnitude factor (frequency-rescaled tables such as
+//                        YaRN's are built on the host: the kernels take the table and the factor).  Only the first `rot_dims` dimensions
+//                        of a head are rotated.
+//   Retention            per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (no softmax, no denominator), then o / rms(o) per head
+//                        and an output gate silu(g).  State [slot][head][dim][vdim] fp32, carried between steps.
+//       prefill          chunks of 32 tokens, three kernels: (1) every chunk's own contribution sum_j decay^(len-1-j) k_j v_j^T in
+//                        parallel, (2) a scan over the chunks of a request that turns them into the state at each chunk's start and
+//                        stores the final state, (3) every chunk's outputs in parallel: decay^(i+1) q_i^T S_start plus the causal
+//                        in-chunk part.  Any start position: the scan starts from the stored state when the request has history.
+//       decode           one kernel: rotate, update the state in place, read out, normalise, gate.
+//   Latent attention     keys and values are up-projections of one cached latent row c (plus one rotated key part shared by all heads).
+//                        The kernels work on the cache directly (absorbed form): score = (W_uk^T q_unrot) . c + q_rot . k_rot, output =
+//                        W_uv (sum_j p_j c_j); the two per-head products run as batched lp_linear calls around lp_latent_attend.
+//                        Sliding window: key j is visible to query i when 0 <= i - j < window (window <= 0: all earlier keys).
+//                        Cache: pages of `page_size` rows [c | k_rot] fp32, one page table row per request.
+//       lp_latent_prep   RMS-norms the latent (vector gain), rotates the shared key part and writes both to the request's pages;
+//                        rotates the query's rotated part in place.
+//       lp_latent_attend one warp per (row, head): online softmax over the visible keys in fp32.
+#include "lp_host.h"
+#include "../../include/leopard_b200.h"
+
+namespace lp {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int RET_CHUNK = LP_RETENTION_CHUNK;
+
+// element d of one head's vector x at position pos: rotated when d < rot_dims, copied otherwise
+__device__ __forceinline__ float rot_elem(const float* __restrict__ x, int d, int rot_dims, int layout, const float* __restrict__ inv_freq,
+                                          float mscale, int pos) {
+  if (d >= rot_dims) return x[d];
+  const int half = rot_dims >> 1;
+  int i, partner;
+  bool first;
+  if (layout == LP_ROT_INTERLEAVED) {
+    i = d >> 1;
+    first = (d & 1) == 0;
+    partner = first ? d + 1 : d - 1;
+  } else {
+    first = d < half;
+    i = first ? d : d - half;
+    partner = first ? d + half : d - half;
+  }
+  const float ang = (float)pos * inv_freq[i];
+  float s, c;
+  sincosf(ang, &s, &c);
+  s *= mscale;
+  c *= mscale;
+  // pair (u, v) -> (u c - v s, v c + u s)
+  return first ? x[d] * c - x[partner] * s : x[d] * c + x[partner] * s;
+}
+
+struct RetArgs {
+  const float* qkvg; long long ld; int q_off, k_off, v_off, g_off;
+  int heads, dim, vdim;
+  const float* decay;
+  const float* inv_freq; int rot_dims, rot_layout; float rot_mscale;
+  float k_scale, eps;
+  float* state; long long slot_stride;
+  void* out; long long ldo; int out_fp32;
+};
+
+// (1) U[chunk][head] = sum_j decay^(len-1-j) k_j v_j^T
+__global__ void __launch_bounds__(128)
+retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
+                             const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, float* __restrict__ ws) {
+  extern __shared__ float dyn_smem[];
+  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int s = chunk_seq[c], row0 = chunk_row0[c], len = chunk_len[c];
+  const int pos0 = seq_pos0[s] + (row0 - seq_row0[s]);
+  float* kd = dyn_smem;                      // [RET_CHUNK][dim]
+  float* vv = dyn_smem + RET_CHUNK * a.dim;  // [RET_CHUNK][vdim]
+  const float dec = a.decay[h];
+  for (int i = tid; i < len * a.dim; i += blockDim.x) {
+    const int j = i / a.dim, d = i % a.dim;
+    const float* kr = a.qkvg + (long long)(row0 + j) * a.ld + a.k_off + h * a.dim;
+    kd[i] = rot_elem(kr, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale * powf(dec, (float)(len - 1 - j));
+  }
+  for (int i = tid; i < len * a.vdim; i += blockDim.x) {
+    const int j = i / a.vdim, d = i % a.vdim;
+    vv[i] = a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d];
+  }
+  __syncthreads();
+  float* U = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
+  for (int i = tid; i < a.dim * a.vdim; i += blockDim.x) {
+    const int x = i / a.vdim, y = i % a.vdim;
+    float acc = 0.f;
+    for (int j = 0; j < len; ++j) acc = fmaf(kd[j * a.dim + x], vv[j * a.vdim + y], acc);
+    U[i] = acc;
+  }
+}
+
+// (2) per (request, head): ws[chunk] <- state at the chunk's start; the state after the last chunk goes to the slot
+__global__ void __launch_bounds__(256)
+retention_scan_kernel(RetArgs a, const int* __restrict__ seq_chunk0, const int* __restrict__ chunk_len, const int* __restrict__ seq_pos0,
+                      const int* __restrict__ seq_slot, float* __restrict__ ws) {
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int c0 = seq_chunk0[s], c1 = seq_chunk0[s + 1];
+  const float dec = a.decay[h];
+  const long long hs = (long long)a.dim * a.vdim;
+  float* st = a.state + (long long)seq_slot[s] * a.slot_stride + h * hs;
+  const bool fresh = seq_pos0[s] == 0;
+  for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+    float S = fresh ? 0.f : st[i];
+    for (int c = c0; c < c1; ++c) {
+      float* u = ws + ((long long)c * a.heads + h) * hs + i;
+      const float own = *u;
+      *u = S;
+      S = fmaf(powf(dec, (float)chunk_len[c]), S, own);
+    }
+    st[i] = S;
+  }
+}
+
+// (3) o_i = decay^(i+1) q_i^T S_start + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j; then o / rms(o) * silu(g)
+__global__ void __launch_bounds__(128)
+retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
+                           const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const float* __restrict__ ws) {
+  extern __shared__ float dyn_smem[];
+  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int s = chunk_seq[c], row0 = chunk_row0[c], len = chunk_len[c];
+  const int pos0 = seq_pos0[s] + (row0 - seq_row0[s]);
+  float* qs = dyn_smem;                        // [RET_CHUNK][dim]
+  float* ks = qs + RET_CHUNK * a.dim;          // [RET_CHUNK][dim]
+  float* vv = ks + RET_CHUNK * a.dim;          // [RET_CHUNK][vdim]
+  float* os = vv + RET_CHUNK * a.vdim;         // [RET_CHUNK][vdim]
+  float* pp = os + RET_CHUNK * a.vdim;         // [RET_CHUNK][RET_CHUNK]
+  float* rr = pp + RET_CHUNK * RET_CHUNK;      // [RET_CHUNK]
+  const float dec = a.decay[h];
+  for (int i = tid; i < len * a.dim; i += blockDim.x) {
+    const int j = i / a.dim, d = i % a.dim;
+    const float* base = a.qkvg + (long long)(row0 + j) * a.ld + h * a.dim;
+    qs[i] = rot_elem(base + a.q_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j);
+    ks[i] = rot_elem(base + a.k_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale;
+  }
+  for (int i = tid; i < len * a.vdim; i += blockDim.x) {
+    const int j = i / a.vdim, d = i % a.vdim;
+    vv[i] = a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d];
+  }
+  __syncthreads();
+  for (int e = tid; e < len * len; e += blockDim.x) {
+    const int i = e / len, j = e % len;
+    float acc = 0.f;
+    if (j <= i) {
+      for (int d = 0; d < a.dim; ++d) acc = fmaf(qs[i * a.dim + d], ks[j * a.dim + d], acc);
+      acc *= powf(dec, (float)(i - j));
+    }
+    pp[i * RET_CHUNK + j] = acc;
+  }
+  __syncthreads();
+  const float* S = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
+  for (int e = tid; e < len * a.vdim; e += blockDim.x) {
+    const int i = e / a.vdim, y = e % a.vdim;
+    float cross = 0.f;
+    for (int d = 0; d < a.dim; ++d) cross = fmaf(qs[i * a.dim + d], S[d * a.vdim + y], cross);
+    float acc = cross * powf(dec, (float)(i + 1));
+    for (int j = 0; j <= i; ++j) acc = fmaf(pp[i * RET_CHUNK + j], vv[j * a.vdim + y], acc);
+    os[e] = acc;
+  }
+  __syncthreads();
+  // one warp per row: root mean square over the head's vdim outputs
+  const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+  for (int i = warp; i < len; i += nwarp) {
+    float ss = 0.f;
+    for (int y = lane; y < a.vdim; y += 32) ss = fmaf(os[i * a.vdim + y], os[i * a.vdim + y], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) rr[i] = 1.0f / sqrtf(ss / (float)a.vdim + a.eps);
+  }
+  __syncthreads();
+  for (int e = tid; e < len * a.vdim; e += blockDim.x) {
+    const int i = e / a.vdim, y = e % a.vdim;
+    const float g = a.qkvg[(long long)(row0 + i) * a.ld + a.g_off + h * a.vdim + y];
+    const float v = os[e] * rr[i] * (g / (1.0f + expf(-g)));
+    const long long o = (long long)(row0 + i) * a.ldo + h * a.vdim + y;
+    if (a.out_fp32) reinterpret_cast<float*>(a.out)[o] = v;
+    else reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16(v);
+  }
+}
+
+// decode: one new row per request.  Threads own state columns; with vdim < blockDim several thread groups split the dim rows.
+constexpr int RET_DEC_THREADS = 128;
+__global__ void __launch_bounds__(RET_DEC_THREADS)
+retention_decode_kernel(RetArgs a, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot) {
+  extern __shared__ float dyn_smem[];
+  const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int row = seq_row0[s], pos = seq_pos0[s];
+  float* qs = dyn_smem;            // [dim]
+  float* ks = qs + a.dim;          // [dim]
+  float* vv = ks + a.dim;          // [vdim]
+  float* os = vv + a.vdim;         // [vdim]
+  float* part = os + a.vdim;       // [groups][vdim]
+  __shared__ float red[RET_DEC_THREADS / 32];
+  const float* base = a.qkvg + (long long)row * a.ld;
+  for (int d = tid; d < a.dim; d += blockDim.x) {
+    qs[d] = rot_elem(base + a.q_off + h * a.dim, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
+    ks[d] = rot_elem(base + a.k_off + h * a.dim, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos) * a.k_scale;
+  }
+  for (int y = tid; y < a.vdim; y += blockDim.x) vv[y] = base[a.v_off + h * a.vdim + y];
+  __syncthreads();
+  const float dec = a.decay[h];
+  const bool fresh = pos == 0;
+  float* st = a.state + (long long)seq_slot[s] * a.slot_stride + (long long)h * a.dim * a.vdim;
+  const int groups = a.vdim >= (int)blockDim.x ? 1 : (int)blockDim.x / a.vdim;
+  const int g = tid / a.vdim;
+  const int per = (a.dim + groups - 1) / groups;
+  if (g < groups) {
+    const int d0 = g * per, d1 = min(a.dim, d0 + per);
+    for (int y = tid % a.vdim; y < a.vdim; y += blockDim.x) {
+      float acc = 0.f;
+      for (int d = d0; d < d1; ++d) {
+        const float old = fresh ? 0.f : st[(long long)d * a.vdim + y];
+        const float S = fmaf(dec, old, ks[d] * vv[y]);
+        st[(long long)d * a.vdim + y] = S;
+        acc = fmaf(S, qs[d], acc);
+      }
+      part[g * a.vdim + y] = acc;
+    }
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int y = tid; y < a.vdim; y += blockDim.x) {
+    float acc = 0.f;
+    for (int gg = 0; gg < groups; ++gg) acc += part[gg * a.vdim + y];
+    os[y] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < RET_DEC_THREADS / 32; ++w) tot += red[w];
+  const float r = 1.0f / sqrtf(tot / (float)a.vdim + a.eps);
+  for (int y = tid; y < a.vdim; y += blockDim.x) {
+    const float gt = base[a.g_off + h * a.vdim + y];
+    const float v = os[y] * r * (gt / (1.0f + expf(-gt)));
+    const long long o = (long long)row * a.ldo + h * a.vdim + y;
+    if (a.out_fp32) reinterpret_cast<float*>(a.out)[o] = v;
+    else reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// latent attention
+// ---------------------------------------------------------------------------------------------------------------------------------
+struct LatArgs {
+  float* q; long long ldq;
+  const float* dkv; long long lddkv;
+  int heads, dim, rot_dim, kv_rank;
+  const float* c_gain; float eps;
+  const float* inv_freq; int rot_dims, rot_layout; float rot_mscale;
+  float* cache; int page_size;
+  const int* page_table; int max_pages;
+  int window; float scale;
+};
+
+__device__ __forceinline__ float* lat_cache_row(const LatArgs& a, int seq, int pos) {
+  const int page = a.page_table[(long long)seq * a.max_pages + pos / a.page_size];
+  return a.cache + ((long long)page * a.page_size + pos % a.page_size) * (a.kv_rank + a.rot_dim);
+}
+
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos) {
+  __shared__ float red[4];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  if (r >= R) return;
+  const int pos = row_pos[r];
+  const float* src = a.dkv + (long long)r * a.lddkv;
+  float ss = 0.f;
+  for (int c = tid; c < a.kv_rank; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)a.kv_rank + a.eps);
+  float* dst = lat_cache_row(a, row_seq[r], pos);
+  for (int c = tid; c < a.kv_rank; c += blockDim.x) dst[c] = src[c] * inv * a.c_gain[c];
+  for (int d = tid; d < a.rot_dim; d += blockDim.x)
+    dst[a.kv_rank + d] = rot_elem(src + a.kv_rank, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
+  // the rotated part of every head's query, in place: one thread per pair reads both members, then writes both
+  float* q = a.q + (long long)r * a.ldq;
+  const int per = a.dim + a.rot_dim, half = a.rot_dims >> 1;
+  for (int p = tid; p < a.heads * half; p += blockDim.x) {
+    float* x = q + (p / half) * per + a.dim;
+    const int i = p % half;
+    const int d0 = a.rot_layout == LP_ROT_INTERLEAVED ? 2 * i : i;
+    const int d1 = a.rot_layout == LP_ROT_INTERLEAVED ? 2 * i + 1 : i + half;
+    const float u = rot_elem(x, d0, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
+    const float v = rot_elem(x, d1, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
+    x[d0] = u;
+    x[d1] = v;
+  }
+}
+
+// One warp per (row, head).  NR = ceil(kv_rank / 32) accumulators per lane.
+constexpr int LAT_WARPS = 4;
+template <int NR>
+__global__ void __launch_bounds__(LAT_WARPS * 32)
+latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, const float* __restrict__ q_abs,
+                     long long ldqa, void* __restrict__ out, long long ldo, int out_fp32) {
+  const int item = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= R * a.heads) return;
+  const int r = item / a.heads, h = item % a.heads;
+  const int seq = row_seq[r], pos = row_pos[r];
+  const float* qa = q_abs + (long long)r * ldqa + (long long)h * a.kv_rank;
+  const float* qr = a.q + (long long)r * a.ldq + (long long)h * (a.dim + a.rot_dim) + a.dim;
+  float qv[NR], acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int c = lane + 32 * i;
+    qv[i] = c < a.kv_rank ? qa[c] : 0.f;
+    acc[i] = 0.f;
+  }
+  // rotated part: rot_dim <= 32 * NR is required by the host; lanes hold it strided as well
+  float qrv[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int c = lane + 32 * i;
+    qrv[i] = c < a.rot_dim ? qr[c] : 0.f;
+  }
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  float mx = -INFINITY, den = 0.f;
+  for (int j = lo; j <= pos; ++j) {
+    const float* kv = lat_cache_row(a, seq, j);
+    float cv[NR];
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int c = lane + 32 * i;
+      cv[i] = c < a.kv_rank ? kv[c] : 0.f;
+      sc = fmaf(qv[i], cv[i], sc);
+      if (c < a.rot_dim) sc = fmaf(qrv[i], kv[a.kv_rank + c], sc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+    sc *= a.scale;
+    const float mn = fmaxf(mx, sc);
+    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the first key
+    const float p = expf(sc - mn);
+    den = den * corr + p;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p, cv[i], acc[i] * corr);
+    mx = mn;
+  }
+  const float inv = 1.0f / den;
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int c = lane + 32 * i;
+    if (c < a.kv_rank) {
+      const long long o = (long long)r * ldo + (long long)h * a.kv_rank + c;
+      if (out_fp32) reinterpret_cast<float*>(out)[o] = acc[i] * inv;
+      else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16(acc[i] * inv);
+    }
+  }
+}
+
+static int fill_ret(RetArgs& a, const lp_retention_desc* d) {
+  LP_REQUIRE(d != nullptr && d->qkvg != nullptr && d->decay != nullptr && d->state != nullptr && d->out != nullptr,
+             "lp_retention: null operand");
+  LP_REQUIRE(d->heads > 0 && d->dim > 0 && d->vdim > 0, "lp_retention: bad sizes heads=%d dim=%d vdim=%d", d->heads, d->dim, d->vdim);
+  LP_REQUIRE(d->rot_dims >= 0 && d->rot_dims <= d->dim && d->rot_dims % 2 == 0, "lp_retention: rot_dims=%d must be even and <= dim=%d",
+             d->rot_dims, d->dim);
+  LP_REQUIRE(d->rot_dims == 0 || d->inv_freq != nullptr, "lp_retention: rotation without a frequency table");
+  a.qkvg = d->qkvg; a.ld = d->ld; a.q_off = d->q_off; a.k_off = d->k_off; a.v_off = d->v_off; a.g_off = d->g_off;
+  a.heads = d->heads; a.dim = d->dim; a.vdim = d->vdim;
+  a.decay = d->decay;
+  a.inv_freq = d->inv_freq; a.rot_dims = d->rot_dims; a.rot_layout = d->rot_layout; a.rot_mscale = d->rot_mscale;
+  a.k_scale = d->k_scale; a.eps = d->eps;
+  a.state = d->state; a.slot_stride = d->slot_stride;
+  a.out = d->out; a.ldo = d->ldo; a.out_fp32 = d->out_fp32;
+  return 0;
+}
+
+static int fill_lat(LatArgs& a, const lp_latent_desc* d) {
+  LP_REQUIRE(d != nullptr && d->q != nullptr && d->cache != nullptr && d->page_table != nullptr, "lp_latent: null operand");
+  LP_REQUIRE(d->heads > 0 && d->dim >= 0 && d->rot_dim >= 0 && d->kv_rank > 0 && d->page_size > 0 && d->max_pages > 0,
+             "lp_latent: bad sizes");
+  LP_REQUIRE(d->rot_dims >= 0 && d->rot_dims <= d->rot_dim && d->rot_dims % 2 == 0, "lp_latent: rot_dims=%d must be even and <= rot_dim=%d",
+             d->rot_dims, d->rot_dim);
+  LP_REQUIRE(d->rot_dims == 0 || d->inv_freq != nullptr, "lp_latent: rotation without a frequency table");
+  a.q = d->q; a.ldq = d->ldq; a.dkv = d->dkv; a.lddkv = d->lddkv;
+  a.heads = d->heads; a.dim = d->dim; a.rot_dim = d->rot_dim; a.kv_rank = d->kv_rank;
+  a.c_gain = d->c_gain; a.eps = d->eps;
+  a.inv_freq = d->inv_freq; a.rot_dims = d->rot_dims; a.rot_layout = d->rot_layout; a.rot_mscale = d->rot_mscale;
+  a.cache = d->cache; a.page_size = d->page_size; a.page_table = d->page_table; a.max_pages = d->max_pages;
+  a.window = d->window; a.scale = d->scale;
+  return 0;
+}
+
+}  // namespace lp
+
+using namespace lp;
+
+extern "C" size_t lp_retention_workspace_bytes(int n_chunks, int heads, int dim, int vdim) {
+  return (size_t)n_chunks * heads * dim * vdim * sizeof(float);
+}
+
+extern "C" int lp_retention_prefill(const lp_retention_desc* d, int n_seqs, int n_chunks, const int* seq_row0, const int* seq_pos0,
+                                    const int* seq_slot, const int* seq_chunk0, const int* chunk_seq, const int* chunk_row0,
+                                    const int* chunk_len, void* ws, size_t ws_bytes, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  RetArgs a;
+  if (int rc = fill_ret(a, d)) return rc;
+  LP_REQUIRE(n_seqs >= 0 && n_chunks >= 0, "lp_retention_prefill: bad counts");
+  if (n_seqs == 0 || n_chunks == 0) return 0;
+  LP_REQUIRE(ws != nullptr && ws_bytes >= lp_retention_workspace_bytes(n_chunks, d->heads, d->dim, d->vdim),
+             "lp_retention_prefill: workspace too small");
+  float* w = reinterpret_cast<float*>(ws);
+  const size_t smem1 = (size_t)RET_CHUNK * (d->dim + d->vdim) * sizeof(float);
+  const size_t smem3 = ((size_t)RET_CHUNK * (2 * d->dim + 2 * d->vdim) + RET_CHUNK * RET_CHUNK + RET_CHUNK) * sizeof(float);
+  LP_REQUIRE(smem3 <= 200 * 1024, "lp_retention_prefill: dim=%d vdim=%d do not fit the chunk kernel's shared memory", d->dim, d->vdim);
+  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
+  retention_chunk_state_kernel<<<dim3(n_chunks, d->heads), 128, smem1, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
+  LP_CHECK_CUDA(cudaGetLastError());
+  retention_scan_kernel<<<dim3(n_seqs, d->heads), 256, 0, stream>>>(a, seq_chunk0, chunk_len, seq_pos0, seq_slot, w);
+  LP_CHECK_CUDA(cudaGetLastError());
+  retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), 128, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
+  LP_CHECK_CUDA(cudaGetLastError());
+  note_launch(3);
+  return 0;
+}
+
+extern "C" int lp_retention_decode(const lp_retention_desc* d, int n_seqs, const int* seq_row0, const int* seq_pos0, const int* seq_slot,
+                                   void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  RetArgs a;
+  if (int rc = fill_ret(a, d)) return rc;
+  if (n_seqs <= 0) return 0;
+  const int groups = d->vdim >= RET_DEC_THREADS ? 1 : RET_DEC_THREADS / d->vdim;
+  const size_t smem = ((size_t)2 * d->dim + 2 * d->vdim + (size_t)groups * d->vdim) * sizeof(float);
+  LP_REQUIRE(smem <= 200 * 1024, "lp_retention_decode: dim=%d vdim=%d do not fit shared memory", d->dim, d->vdim);
+  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  retention_decode_kernel<<<dim3(n_seqs, d->heads), RET_DEC_THREADS, smem, stream>>>(a, seq_row0, seq_pos0, seq_slot);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_latent_prep(const lp_latent_desc* d, int R, const int* row_seq, const int* row_pos, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LatArgs a;
+  if (int rc = fill_lat(a, d)) return rc;
+  LP_REQUIRE(d->dkv != nullptr && d->c_gain != nullptr && row_seq != nullptr && row_pos != nullptr, "lp_latent_prep: null operand");
+  if (R <= 0) return 0;
+  latent_prep_kernel<<<R, 128, 0, stream>>>(a, R, row_seq, row_pos);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_latent_attend(const lp_latent_desc* d, int R, const int* row_seq, const int* row_pos, const float* q_abs, long long ldqa,
+                                void* out, long long ldo, int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LatArgs a;
+  if (int rc = fill_lat(a, d)) return rc;
+  LP_REQUIRE(q_abs != nullptr && out != nullptr && row_seq != nullptr && row_pos != nullptr, "lp_latent_attend: null operand");
+  LP_REQUIRE(d->rot_dim <= d->kv_rank || d->rot_dim <= 32, "lp_latent_attend: rot_dim=%d must not exceed kv_rank=%d", d->rot_dim, d->kv_rank);
+  LP_REQUIRE(d->kv_rank <= 1024, "lp_latent_attend: kv_rank=%d > 1024 is not instantiated", d->kv_rank);
+  if (R <= 0) return 0;
+  const int nr = (d->kv_rank + 31) / 32;
+  const unsigned grid = (unsigned)(((long long)R * d->heads + LAT_WARPS - 1) / LAT_WARPS);
+  if (nr <= 2) latent_attend_kernel<2><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  else if (nr <= 4) latent_attend_kernel<4><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  else if (nr <= 8) latent_attend_kernel<8><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  else if (nr <= 16) latent_attend_kernel<16><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  else latent_attend_kernel<32><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

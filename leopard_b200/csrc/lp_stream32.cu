@@ -1,0 +1,121 @@
+// leopard_b200 — glue kernels of models whose residual stream is kept in 32-bit floats.
+//
+//   lp_embed_rows_f32   x[r, :] = table[ids[r], :]  (bf16 table -> fp32 rows)
+//   lp_rmsnorm_f32      y = x / sqrt(mean(x^2) + eps) * g over fp32 rows, eps inside the root; g is one number (gain_scalar), a vector
+//                       (gain_vec) or both.  The result is written as fp32 or bf16 (the operand of the next matrix product), or — with
+//                       `accum` — added to another fp32 matrix: the sandwich-norm residual update x <- x + norm(sublayer(x)) in one pass.
+//   lp_glu_f32          elementwise epilogues for matrix products that ran elsewhere: xIELU, silu(gate) * up.
+//
+// One warp per row, statistics and normalisation in fp32; the row is read twice (the second read hits L1 / L2).
+#include "lp_host.h"
+#include "../../include/leopard_b200.h"
+
+namespace lp {
+
+typedef __nv_bfloat16 bf16;
+
+__global__ void embed_rows_f32_kernel(const int* __restrict__ ids, int R, const bf16* __restrict__ table, long long ldt, int vocab,
+                                      float* __restrict__ out, long long ldo, int D) {
+  const int r = blockIdx.x;
+  if (r >= R) return;
+  int id = ids[r];
+  if (id < 0 || id >= vocab) id = 0;   // the host validates ids; this only keeps a bad one inside the table
+  const bf16* src = table + (long long)id * ldt;
+  float* dst = out + (long long)r * ldo;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = __bfloat162float(src[c]);
+}
+
+constexpr int NORM32_WARPS = 8;
+__global__ void __launch_bounds__(NORM32_WARPS * 32)
+rmsnorm_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, float gain_scalar, const float* __restrict__ gain_vec,
+                   float eps, float* __restrict__ out_f32, bf16* __restrict__ out_bf16, long long ldo, float* __restrict__ accum,
+                   long long lda) {
+  const int row = blockIdx.x * NORM32_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float* xr = x + (long long)row * ldx;
+  float ss = 0.f;
+  for (int c = lane; c < D; c += 32) {
+    const float v = xr[c];
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int c = lane; c < D; c += 32) {
+    float v = xr[c] * r * gain_scalar;
+    if (gain_vec != nullptr) v *= gain_vec[c];
+    if (accum != nullptr) accum[(long long)row * lda + c] += v;
+    else if (out_f32 != nullptr) out_f32[(long long)row * ldo + c] = v;
+    else out_bf16[(long long)row * ldo + c] = __float2bfloat16(v);
+  }
+}
+
+template <typename T> __device__ __forceinline__ float ld32(const T* p);
+template <> __device__ __forceinline__ float ld32<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ld32<bf16>(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st32(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st32(bf16* p, float v) { *p = __float2bfloat16(v); }
+
+// mode LP_EPI_XIELU: out[m, n] = xielu(in[m, n]); LP_EPI_SILU_GATE: out[m, n] = silu(in[m, n]) * in[m, n + N]
+template <typename IT, typename OT>
+__global__ void glu_kernel(const IT* __restrict__ in, long long ldi, OT* __restrict__ out, long long ldo, int M, int N, int mode, float a,
+                           float b) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  const float z = ld32<IT>(in + (long long)m * ldi + n);
+  float v;
+  if (mode == LP_EPI_SILU_GATE) v = z / (1.0f + expf(-z)) * ld32<IT>(in + (long long)m * ldi + n + N);
+  else v = z > 0.f ? a * z * z + 0.5f * z : b * (expm1f(z) - z) + 0.5f * z;
+  st32(out + (long long)m * ldo + n, v);
+}
+
+}  // namespace lp
+
+using namespace lp;
+
+extern "C" int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float* out, long long ldo, int D,
+                                 void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(ids != nullptr && table != nullptr && out != nullptr && R >= 0 && D > 0 && vocab > 0, "lp_embed_rows_f32: bad arguments");
+  if (R == 0) return 0;
+  embed_rows_f32_kernel<<<R, 128, 0, stream>>>(ids, R, reinterpret_cast<const bf16*>(table), ldt, vocab, out, ldo, D);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_rmsnorm_f32(const float* x, long long ldx, int M, int D, float gain_scalar, const float* gain_vec, float eps, void* out,
+                              long long ldo, int out_fp32, float* accum, long long ld_accum, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && M >= 0 && D > 0, "lp_rmsnorm_f32: bad arguments");
+  LP_REQUIRE((out != nullptr) != (accum != nullptr), "lp_rmsnorm_f32: give either `out` or `accum`");
+  if (M == 0) return 0;
+  rmsnorm_f32_kernel<<<(M + NORM32_WARPS - 1) / NORM32_WARPS, NORM32_WARPS * 32, 0, stream>>>(
+      x, ldx, M, D, gain_scalar, gain_vec, eps, (out != nullptr && out_fp32) ? reinterpret_cast<float*>(out) : nullptr,
+      (out != nullptr && !out_fp32) ? reinterpret_cast<bf16*>(out) : nullptr, ldo, accum, ld_accum);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode,
+                          float a, float b, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(in != nullptr && out != nullptr && M >= 0 && N > 0, "lp_glu_f32: bad arguments");
+  LP_REQUIRE(mode == LP_EPI_XIELU || mode == LP_EPI_SILU_GATE, "lp_glu_f32: mode %d is not an activation", mode);
+  if (M == 0) return 0;
+  const unsigned grid = (unsigned)(((long long)M * N + 255) / 256);
+  if (in_fp32 && out_fp32)
+    glu_kernel<float, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b);
+  else if (in_fp32)
+    glu_kernel<float, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b);
+  else if (out_fp32)
+    glu_kernel<bf16, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b);
+  else
+    glu_kernel<bf16, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

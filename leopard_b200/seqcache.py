@@ -1,0 +1,120 @@
+"""Cache and state manager of the decoder-only language models (leopard_b200/seqlm.py).
+
+Two kinds of per-request memory, both owned here and handed to the kernels as pools plus small index tables:
+
+* a PAGED row cache for attention layers: pages of `page_size` token rows; every caching layer has its own pool
+  [pages, page_size, row width] fp32 and all layers share one page numbering, so a request needs one page table.  Layers with a
+  sliding window never look further back than their window, so pages that have fallen out of every layer's window are given back
+  while the request is still running: a windowed model's cache per request is bounded by its largest window, not by its length.
+* a SLOT pool for recurrent layers: one fp32 state [heads, dim, vdim] per (layer, slot).  A slot is not cleared when it is handed
+  out again: the kernels start a request at position 0 from a zero state without reading the slot.
+
+Pools grow (by reallocation) when a batch needs more than the configured size; `max_tokens` only sizes the first allocation.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence as Seq
+
+import torch
+
+
+@dataclass
+class Sequence:
+    key: Hashable
+    slot: int
+    length: int = 0                       # tokens already in the cache / state
+    pages: List[int] = field(default_factory=list)   # page of logical block i, -1 once it has been given back
+
+
+class SequenceCache:
+    def __init__(self, row_widths: Seq[int], state_shapes: Seq[Seq[int]], window: Optional[int], device, max_tokens: int = 4096,
+                 page_size: int = 64, max_seqs: int = 8):
+        """row_widths[i]: floats per token of caching layer i; state_shapes[j]: state shape of recurrent layer j;
+        window: the largest look-back (tokens, the current one included) of all caching layers, None if one of them sees everything."""
+        if page_size <= 0:
+            raise ValueError("page_size must be positive")
+        self.device = torch.device(device)
+        self.page_size = int(page_size)
+        self.window = window
+        self.row_widths = [int(w) for w in row_widths]
+        self.state_shapes = [tuple(int(x) for x in s) for s in state_shapes]
+        self.n_pages = 0
+        self.n_slots = 0
+        self.pools: List[torch.Tensor] = [torch.empty((0, self.page_size, w), dtype=torch.float32, device=self.device) for w in self.row_widths]
+        self.states: List[torch.Tensor] = [torch.empty((0, *s), dtype=torch.float32, device=self.device) for s in self.state_shapes]
+        self.free_pages: List[int] = []
+        self.free_slots: List[int] = []
+        self.seqs: Dict[Hashable, Sequence] = {}
+        self.generation = 0                # bumped whenever a pool is reallocated (captured pointers become stale)
+        if self.row_widths:
+            self._grow_pages(-(-max(int(max_tokens), 1) // self.page_size) + max_seqs)
+        self._grow_slots(max_seqs)
+
+    # ------------------------------------------------------------------ pools
+    def _grow_pages(self, n_new: int):
+        total = self.n_pages + n_new
+        for i, w in enumerate(self.row_widths):
+            pool = torch.empty((total, self.page_size, w), dtype=torch.float32, device=self.device)
+            if self.n_pages:
+                pool[: self.n_pages].copy_(self.pools[i])
+            self.pools[i] = pool
+        self.free_pages.extend(range(total - 1, self.n_pages - 1, -1))   # pop() hands out low numbers first
+        self.n_pages = total
+        self.generation += 1
+
+    def _grow_slots(self, n_new: int):
+        total = self.n_slots + n_new
+        for j, s in enumerate(self.state_shapes):
+            st = torch.zeros((total, *s), dtype=torch.float32, device=self.device)
+            if self.n_slots:
+                st[: self.n_slots].copy_(self.states[j])
+            self.states[j] = st
+        self.free_slots.extend(range(total - 1, self.n_slots - 1, -1))
+        self.n_slots = total
+        self.generation += 1
+
+    # ------------------------------------------------------------------ requests
+    def open(self, key: Hashable) -> Sequence:
+        if key in self.seqs:
+            raise KeyError(f"request {key!r} is already open")
+        if not self.free_slots:
+            self._grow_slots(max(4, self.n_slots))
+        seq = Sequence(key=key, slot=self.free_slots.pop())
+        self.seqs[key] = seq
+        return seq
+
+    def get(self, key: Hashable) -> Optional[Sequence]:
+        return self.seqs.get(key)
+
+    def reserve(self, seq: Sequence, n_tokens: int) -> None:
+        """Make sure pages exist for positions [seq.length, seq.length + n_tokens)."""
+        if not self.row_widths:
+            return
+        need = -(-(seq.length + n_tokens) // self.page_size)
+        while len(seq.pages) < need:
+            if not self.free_pages:
+                self._grow_pages(max(8, self.n_pages // 2))
+            seq.pages.append(self.free_pages.pop())
+
+    def advance(self, seq: Sequence, n_tokens: int) -> None:
+        """The step wrote n_tokens more; pages that no later query can see go back to the pool."""
+        seq.length += n_tokens
+        if self.window is None or not self.row_widths:
+            return
+        first_needed = seq.length - self.window + 1          # the oldest position the NEXT query (at seq.length) sees
+        for b in range(min(len(seq.pages), max(first_needed, 0) // self.page_size)):
+            if seq.pages[b] >= 0:
+                self.free_pages.append(seq.pages[b])
+                seq.pages[b] = -1
+
+    def close(self, key: Hashable) -> None:
+        seq = self.seqs.pop(key)
+        self.free_pages.extend(p for p in seq.pages if p >= 0)
+        self.free_slots.append(seq.slot)
+
+    def live_tokens(self) -> int:
+        return sum(s.length for s in self.seqs.values())
+
+    def pages_in_use(self) -> int:
+        return self.n_pages - len(self.free_pages)
