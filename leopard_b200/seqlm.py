@@ -184,7 +184,11 @@ class SeqLMWeights:
                 lw["act_a"], lw["act_b"] = softplus(float(act[0])), 0.5 + softplus(float(act[1]))
             elif isinstance(f, MoEConfig):
                 lw["w_router"] = mat(w(i, "mlp.router", (f.experts, D)))
-                lw["correction"] = w(i, "mlp.correction", (f.experts,)).float().contiguous().to(dev)
+                try:
+                    corr = w(i, "mlp.correction", (f.experts,)).float()
+                except KeyError:                     # a router without a choice bias
+                    corr = torch.zeros(f.experts)
+                lw["correction"] = corr.contiguous().to(dev)
                 gu = [torch.cat([w(i, f"mlp.e{e}.gate", (f.expert_ff, D)), w(i, f"mlp.e{e}.up", (f.expert_ff, D))], 0)
                       for e in range(f.experts)]
                 lw["w_gu"] = mat(torch.stack(gu, 0))                                           # [experts][2 ff, D]
