@@ -568,8 +568,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg2", "cfg4", "cfg5"],
-                    help="cfg3 (default) = the metric's configuration; cfg2 = 1 x 1344^2; cfg4 = Idefics2 8 x 980^2; cfg5 = SFT step")
+    ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg2", "cfg4", "cfg5", "seqlm"],
+                    help="cfg3 (default) = the metric's configuration; cfg2 = 1 x 1344^2; cfg4 = Idefics2 8 x 980^2; cfg5 = SFT step; "
+                         "seqlm = prefill / decode of the layer-list language models beside the Llama-style decoder at equal size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the library / strong-scaling / decode / front-end legs")
     ap.add_argument("--quick", action="store_true", help="1 warm-up, timed loop only (for runs under ncu)")
@@ -584,6 +585,9 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", __file__] + sys.argv[1:]
         return subprocess.call(cmd)
+    if args.workload == "seqlm":
+        from benchmarks import seqlm_bench
+        return seqlm_bench.run(args)
     if args.workload in ("cfg4", "cfg5"):
         from benchmarks import other_workloads
         return other_workloads.run(args)

@@ -248,6 +248,7 @@ STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_li
                     "lp_embed_rows_f32", "lp_rmsnorm_f32", "lp_glu_f32", "lp_retention_workspace_bytes", "lp_retention_prefill",
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
                     "lp_moe_combine")
+STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None
 
 
@@ -260,6 +261,10 @@ def bind_stream32(L):
         except AttributeError as e:
             raise NativeError(f"the library does not export {name}: rebuild it") from e
         fn.restype, fn.argtypes = _SIGS[name]
+    for name in STREAM32_OPTIONAL:
+        if hasattr(L, name):
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = _SIGS[name]
     return L
 
 

@@ -27,6 +27,7 @@ from . import _lib
 from .seqcache import SequenceCache
 
 F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
+TENSOR_CORE_MIN_ROWS = 128
 
 
 # ---------------------------------------------------------------------------------------------------------------- configuration
@@ -294,6 +295,8 @@ class SeqLMEngine:
             self._state_index.append(-1 if is_lat else b)
             a, b = a + is_lat, b + (not is_lat)
         self.tile_rows = int(self.L.lp_linear_tile_rows())
+        # large bf16 products of the serving precision go to the tcgen05 GEMM when the library has it (the native ones do)
+        self.tensor_core_rows = TENSOR_CORE_MIN_ROWS if dtype == "bfloat16" and hasattr(self.L, "lp_gemm_bf16") else None
         self.tap: Optional[Callable[[int, torch.Tensor], None]] = None   # called with (layer, residual stream) after every layer
 
     # ------------------------------------------------------------------ helpers
@@ -306,6 +309,12 @@ class SeqLMEngine:
     def _empty(self, shape, dtype):
         return torch.empty(shape, dtype=dtype, device=self.device)
 
+    def _on_tensor_cores(self, a, w, M, N, K) -> bool:
+        """The tcgen05 GEMM takes a product when it is large enough to fill tiles and meets the 16-byte rules of its TMA loads."""
+        return (self.tensor_core_rows is not None and M >= self.tensor_core_rows and a.dtype == BF16 and N >= 128 and K >= 64
+                and N % 8 == 0 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
     def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0, out=None):
         """out[M, N'] = epi(a[M, K] @ w[N, K].T)."""
         M, K = a.shape
@@ -313,6 +322,16 @@ class SeqLMEngine:
         n_out = N // 2 if epi == _lib.EPI_SILU_GATE else N
         if out is None:
             out = self._empty((M, n_out), out_dtype)
+        if self._on_tensor_cores(a, w, M, N, K) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+            raw = out if epi == _lib.EPI_NONE else self._empty((M, N), F32)
+            rc = self.L.lp_gemm_bf16(_lib.ptr(a), a.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(raw), raw.stride(0), M, N, K, None, None,
+                                     0, 0, _lib.ACT_NONE, int(raw.dtype == F32), 0, self._stream())
+            self._check(rc, "lp_gemm_bf16")
+            if epi != _lib.EPI_NONE:
+                rc = self.L.lp_glu_f32(_lib.ptr(raw), raw.stride(0), 1, _lib.ptr(out), out.stride(0), int(out.dtype == F32), M, n_out, epi,
+                                       epi_a, epi_b, self._stream())
+                self._check(rc, "lp_glu_f32")
+            return out
         d = _lib.LinearDesc(A=_lib.ptr(a), lda=a.stride(0), a_batch=0, a_fp32=int(a.dtype == F32), W=_lib.ptr(w), ldw=w.stride(0),
                             w_batch=0, C=_lib.ptr(out), ldc=out.stride(0), c_batch=0, c_fp32=int(out.dtype == F32), M=M, N=N, K=K,
                             batch=1, epi=epi, epi_a=epi_a, epi_b=epi_b)

@@ -137,3 +137,26 @@ def test_feed_forward_alone(backend, T, ff):
     f, lw = eng.cfg.layers[0].ff, eng.w.layers[0]
     got = eng._dense(f, lw, h.to(device)) if ff["kind"] == "dense" else eng._moe(f, lw, h.to(device))
     assert rel_err(got, want) < 1e-5
+
+
+@pytest.mark.gpu
+def test_large_bf16_products_run_on_the_tensor_cores():
+    """in the serving precision a product of 128 rows or more goes to the tcgen05 GEMM; same result as the fp32-FMA kernels up to
+    the rounding of the accumulation order, ragged N and K included, with and without an epilogue"""
+    cfg = model([retention_layer()])
+    w = O.random_weights(cfg, seed=2)
+    eng = make_engine(cfg, w, ("cuda", None), "bfloat16")
+    assert eng.tensor_core_rows == 128
+    g = torch.Generator().manual_seed(5)
+    for M, N, K in ((130, 128, 64), (333, 328, 136), (1000, 784, 320)):
+        a = torch.randn(M, K, generator=g).to(BF16).cuda()
+        wt = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(BF16).cuda()
+        want = a.double() @ wt.double().T
+        assert eng._on_tensor_cores(a, wt, M, N, K)
+        for c_dt, tol in ((F32, 1e-5), (BF16, 1e-2)):
+            assert rel_err(eng.linear(a, wt, c_dt), want) < tol, (M, N, K, c_dt)
+        gate, up = want[:, : N // 2], want[:, N // 2:]
+        assert rel_err(eng.linear(a, wt, F32, _lib.EPI_SILU_GATE), gate * torch.sigmoid(gate) * up) < 1e-5
+        eng.tensor_core_rows = None                 # the same call on the fp32-FMA kernel
+        assert rel_err(eng.linear(a, wt, F32), want) < 1e-5
+        eng.tensor_core_rows = 128
