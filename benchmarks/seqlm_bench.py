@@ -226,7 +226,7 @@ def bench_llama_twin(name, s, dev, steps, warmup, prompt):
     from leopard_b200.engine import PrefillEngine
     from leopard_b200.native_weights import random_native
     cfg = reduced(leopard_llava(), vit_layers=1, dec_layers=4, vocab=s["vocab"])
-    cfg = replace(cfg, dec=replace(cfg.dec, hidden=s["width"], ffn=s["ff"], heads=s["heads"], kv_heads=s["heads"]))
+    cfg = replace(cfg, dec=replace(cfg.dec, hidden=s["width"], ffn=s["ff"], heads=s["heads"], kv_heads=s["heads"] // 4))      # the Llama path is built for 4 query heads per kv head
     eng = PrefillEngine(cfg, random_native(cfg, dev, seed=7))
     ids = torch.randint(0, s["vocab"] - 100, (prompt,), generator=torch.Generator().manual_seed(0))
     out = {"size": name}

@@ -36,6 +36,14 @@ __device__ __forceinline__ float lin_load(const bf16* p) { return __bfloat162flo
 __device__ __forceinline__ void lin_store(float* p, float v) { *p = v; }
 __device__ __forceinline__ void lin_store(bf16* p, float v) { *p = __float2bfloat16(v); }
 
+// eight bf16 values of a 16-byte load -> fp32 (a bf16 is the upper half of an fp32)
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+
 // xIELU with a = softplus(p), b = 1/2 + softplus(q):  z > 0: a z^2 + z/2;  z <= 0: b (exp(z) - 1 - z) + z/2
 __device__ __forceinline__ float xielu_f(float z, float a, float b) {
   return z > 0.f ? a * z * z + 0.5f * z : b * (expm1f(z) - z) + 0.5f * z;
@@ -149,14 +157,9 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
       const uint4 u1 = *reinterpret_cast<const uint4*>(w1 + k);
       uint4 u2 = u1;
       if (GATED) u2 = *reinterpret_cast<const uint4*>(w2 + k);
-      const bf16* p1 = reinterpret_cast<const bf16*>(&u1);
-      const bf16* p2 = reinterpret_cast<const bf16*>(&u2);
       float f1[8], f2[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        f1[i] = __bfloat162float(p1[i]);
-        f2[i] = __bfloat162float(p2[i]);
-      }
+      bf16x8_to_f32(u1, f1);
+      bf16x8_to_f32(u2, f2);
 #pragma unroll
       for (int m = 0; m < ROWS_MAX; ++m) {
         if (m < a.M) {

@@ -18,44 +18,63 @@ namespace lp {
 typedef __nv_bfloat16 bf16;
 
 constexpr int MOE_MAX_EXPERTS = 512;
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
+
+// eight bf16 values of a 16-byte load -> fp32 (a bf16 is the upper half of an fp32)
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
 
 template <typename HT> __device__ __forceinline__ float moe_ld(const HT* p);
 template <> __device__ __forceinline__ float moe_ld<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float moe_ld<bf16>(const bf16* p) { return __bfloat162float(*p); }
 
+// One CTA per token: the warps share out the router rows (and the gate row), 16-byte loads of the bf16 weights when the width
+// allows; then one thread makes the choice among the E scores.
 template <typename HT>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf16* __restrict__ w_router, long long ldw, int E,
                  const float* __restrict__ correction, int n_groups, int keep_groups, int top, const bf16* __restrict__ w_gate,
                  int* __restrict__ idx_out, float* __restrict__ w_out, float* __restrict__ gate_out) {
-  __shared__ float s_sc[ROUTE_WARPS][MOE_MAX_EXPERTS];   // sigmoid scores
-  __shared__ float s_ch[ROUTE_WARPS][MOE_MAX_EXPERTS];   // choice scores (minus infinity once taken or not eligible)
+  __shared__ float sc[MOE_MAX_EXPERTS];   // sigmoid scores
+  __shared__ float ch[MOE_MAX_EXPERTS];   // choice scores (minus infinity once taken or not eligible)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  const int t = blockIdx.x;
   if (t >= T) return;
   const HT* hr = h + (long long)t * ldh;
-  for (int e = 0; e <= E; ++e) {
+  const bool vec = (D % 8 == 0) && (ldw % 8 == 0) && ((reinterpret_cast<uintptr_t>(w_router) & 15) == 0) &&
+                   (w_gate == nullptr || (reinterpret_cast<uintptr_t>(w_gate) & 15) == 0);
+  for (int e = warp; e <= E; e += ROUTE_WARPS) {
     if (e == E && w_gate == nullptr) break;
     const bf16* wr = e < E ? w_router + (long long)e * ldw : w_gate;
     float acc = 0.f;
-    for (int c = lane; c < D; c += 32) acc = fmaf(moe_ld<HT>(hr + c), __bfloat162float(wr[c]), acc);
+    if (vec) {
+      for (int c = lane * 8; c < D; c += 256) {
+        float f[8];
+        bf16x8_to_f32(*reinterpret_cast<const uint4*>(wr + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(moe_ld<HT>(hr + c + i), f[i], acc);
+      }
+    } else {
+      for (int c = lane; c < D; c += 32) acc = fmaf(moe_ld<HT>(hr + c), __bfloat162float(wr[c]), acc);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     const float s = 1.0f / (1.0f + expf(-acc));
     if (lane == 0) {
       if (e < E) {
-        s_sc[warp][e] = s;
-        s_ch[warp][e] = s + (correction != nullptr ? correction[e] : 0.f);
+        sc[e] = s;
+        ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
       } else {
         gate_out[t] = s;
       }
     }
   }
-  __syncwarp();
-  if (lane != 0) return;
-  float* sc = s_sc[warp];
-  float* ch = s_ch[warp];
+  __syncthreads();
+  if (threadIdx.x != 0) return;
   if (n_groups > 1 && keep_groups < n_groups) {
     const int gs = E / n_groups;
     // group score: the sum of the two largest choice scores (of the only one when groups hold a single expert)
@@ -155,7 +174,7 @@ extern "C" int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int
              E / n_groups, top);
   LP_REQUIRE(w_gate == nullptr || gate_out != nullptr, "lp_moe_route: gate weights without an output");
   if (T <= 0) return 0;
-  const unsigned grid = (T + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  const unsigned grid = (unsigned)T;
   if (h_fp32)
     moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const float*>(h), ldh, T, D,
         reinterpret_cast<const bf16*>(w_router), ldw, E, correction, n_groups, keep_groups, top, reinterpret_cast<const bf16*>(w_gate),

@@ -18,7 +18,7 @@
 //                        Cache: pages of `page_size` rows [c | k_rot] fp32, one page table row per request.
 //       lp_latent_prep   RMS-norms the latent (vector gain), rotates the shared key part and writes both to the request's pages;
 //                        rotates the query's rotated part in place.
-//       lp_latent_attend one warp per (row, head): online softmax over the visible keys in fp32.
+//       lp_latent_attend one CTA per (row, head), its warps split the visible keys: online softmax in fp32, merged at the end.
 #include "lp_host.h"
 #include "../../include/leopard_b200.h"
 
@@ -63,7 +63,8 @@ struct RetArgs {
   void* out; long long ldo; int out_fp32;
 };
 
-// (1) U[chunk][head] = sum_j decay^(len-1-j) k_j v_j^T
+// (1) U[chunk][head] = sum_j decay^(len-1-j) k_j v_j^T.  4 x 4 outputs per thread; a thread's four columns are vdim/4 apart, so that
+// the threads of a warp read consecutive shared-memory words.
 __global__ void __launch_bounds__(128)
 retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
                              const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, float* __restrict__ ws) {
@@ -71,25 +72,52 @@ retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int s = chunk_seq[c], row0 = chunk_row0[c], len = chunk_len[c];
   const int pos0 = seq_pos0[s] + (row0 - seq_row0[s]);
-  float* kd = dyn_smem;                      // [RET_CHUNK][dim]
-  float* vv = dyn_smem + RET_CHUNK * a.dim;  // [RET_CHUNK][vdim]
+  const int dimp = ((a.dim + 3) & ~3) + 1, vdimp = (a.vdim + 3) & ~3;      // padded rows: whole 4-tiles, odd stride for k
+  float* kd = dyn_smem;                   // [RET_CHUNK][dimp]
+  float* vv = kd + RET_CHUNK * dimp;      // [RET_CHUNK][vdimp]
   const float dec = a.decay[h];
-  for (int i = tid; i < len * a.dim; i += blockDim.x) {
-    const int j = i / a.dim, d = i % a.dim;
-    const float* kr = a.qkvg + (long long)(row0 + j) * a.ld + a.k_off + h * a.dim;
-    kd[i] = rot_elem(kr, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale * powf(dec, (float)(len - 1 - j));
+  for (int i = tid; i < len * dimp; i += blockDim.x) {
+    const int j = i / dimp, d = i % dimp;
+    float v = 0.f;
+    if (d < a.dim) {
+      const float* kr = a.qkvg + (long long)(row0 + j) * a.ld + a.k_off + h * a.dim;
+      v = rot_elem(kr, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale * powf(dec, (float)(len - 1 - j));
+    }
+    kd[i] = v;
   }
-  for (int i = tid; i < len * a.vdim; i += blockDim.x) {
-    const int j = i / a.vdim, d = i % a.vdim;
-    vv[i] = a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d];
+  for (int i = tid; i < len * vdimp; i += blockDim.x) {
+    const int j = i / vdimp, d = i % vdimp;
+    vv[i] = d < a.vdim ? a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d] : 0.f;
   }
   __syncthreads();
   float* U = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
-  for (int i = tid; i < a.dim * a.vdim; i += blockDim.x) {
-    const int x = i / a.vdim, y = i % a.vdim;
-    float acc = 0.f;
-    for (int j = 0; j < len; ++j) acc = fmaf(kd[j * a.dim + x], vv[j * a.vdim + y], acc);
-    U[i] = acc;
+  const int tiles_y = vdimp >> 2, tiles_x = (a.dim + 3) >> 2;
+  for (int tile = tid; tile < tiles_x * tiles_y; tile += blockDim.x) {
+    const int x0 = (tile / tiles_y) * 4, ty = tile % tiles_y;
+    float acc[4][4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[p][q] = 0.f;
+    for (int j = 0; j < len; ++j) {
+      float k4[4], v4[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        k4[p] = kd[j * dimp + x0 + p];
+        v4[p] = vv[j * vdimp + ty + p * tiles_y];
+      }
+#pragma unroll
+      for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(k4[p], v4[q], acc[p][q]);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int x = x0 + p, y = ty + q * tiles_y;
+        if (x < a.dim && y < a.vdim) U[x * a.vdim + y] = acc[p][q];
+      }
   }
 }
 
@@ -115,57 +143,126 @@ retention_scan_kernel(RetArgs a, const int* __restrict__ seq_chunk0, const int* 
   }
 }
 
-// (3) o_i = decay^(i+1) q_i^T S_start + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j; then o / rms(o) * silu(g)
+// (3) o_i = decay^(i+1) q_i^T S_start + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j; then o / rms(o) * silu(g).  The chunk's start state is
+// staged in shared memory (stage_s; read from global when a head is too large for that); 4 x 4 outputs per thread.
 __global__ void __launch_bounds__(128)
 retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
-                           const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const float* __restrict__ ws) {
+                           const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const float* __restrict__ ws, int stage_s) {
   extern __shared__ float dyn_smem[];
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int s = chunk_seq[c], row0 = chunk_row0[c], len = chunk_len[c];
   const int pos0 = seq_pos0[s] + (row0 - seq_row0[s]);
-  float* qs = dyn_smem;                        // [RET_CHUNK][dim]
-  float* ks = qs + RET_CHUNK * a.dim;          // [RET_CHUNK][dim]
-  float* vv = ks + RET_CHUNK * a.dim;          // [RET_CHUNK][vdim]
-  float* os = vv + RET_CHUNK * a.vdim;         // [RET_CHUNK][vdim]
-  float* pp = os + RET_CHUNK * a.vdim;         // [RET_CHUNK][RET_CHUNK]
-  float* rr = pp + RET_CHUNK * RET_CHUNK;      // [RET_CHUNK]
+  const int dimp = ((a.dim + 3) & ~3) + 1, vdimp = (a.vdim + 3) & ~3;
+  float* qs = dyn_smem;                        // [RET_CHUNK][dimp]
+  float* ks = qs + RET_CHUNK * dimp;           // [RET_CHUNK][dimp]
+  float* vv = ks + RET_CHUNK * dimp;           // [RET_CHUNK][vdimp]
+  float* os = vv + RET_CHUNK * vdimp;          // [RET_CHUNK][vdimp]
+  float* pp = os + RET_CHUNK * vdimp;          // [RET_CHUNK][RET_CHUNK + 1]
+  float* rr = pp + RET_CHUNK * (RET_CHUNK + 1);   // [RET_CHUNK]
+  float* Ss = rr + RET_CHUNK;                  // [dim][vdimp] when stage_s
   const float dec = a.decay[h];
-  for (int i = tid; i < len * a.dim; i += blockDim.x) {
-    const int j = i / a.dim, d = i % a.dim;
-    const float* base = a.qkvg + (long long)(row0 + j) * a.ld + h * a.dim;
-    qs[i] = rot_elem(base + a.q_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j);
-    ks[i] = rot_elem(base + a.k_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale;
-  }
-  for (int i = tid; i < len * a.vdim; i += blockDim.x) {
-    const int j = i / a.vdim, d = i % a.vdim;
-    vv[i] = a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d];
-  }
-  __syncthreads();
-  for (int e = tid; e < len * len; e += blockDim.x) {
-    const int i = e / len, j = e % len;
-    float acc = 0.f;
-    if (j <= i) {
-      for (int d = 0; d < a.dim; ++d) acc = fmaf(qs[i * a.dim + d], ks[j * a.dim + d], acc);
-      acc *= powf(dec, (float)(i - j));
+  for (int i = tid; i < RET_CHUNK * dimp; i += blockDim.x) {
+    const int j = i / dimp, d = i % dimp;
+    float qv = 0.f, kv = 0.f;
+    if (j < len && d < a.dim) {
+      const float* base = a.qkvg + (long long)(row0 + j) * a.ld + h * a.dim;
+      qv = rot_elem(base + a.q_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j);
+      kv = rot_elem(base + a.k_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale;
     }
-    pp[i * RET_CHUNK + j] = acc;
+    qs[i] = qv;
+    ks[i] = kv;
+  }
+  for (int i = tid; i < RET_CHUNK * vdimp; i += blockDim.x) {
+    const int j = i / vdimp, d = i % vdimp;
+    vv[i] = (j < len && d < a.vdim) ? a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d] : 0.f;
+  }
+  const float* S = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
+  if (stage_s)
+    for (int i = tid; i < a.dim * vdimp; i += blockDim.x) {
+      const int d = i / vdimp, y = i % vdimp;
+      Ss[i] = y < a.vdim ? S[d * a.vdim + y] : 0.f;
+    }
+  __syncthreads();
+  // in-chunk scores, 4 x 4 per thread (rows i0 .. i0+3, columns tj, tj+8, tj+16, tj+24)
+  for (int tile = tid; tile < (RET_CHUNK / 4) * (RET_CHUNK / 4); tile += blockDim.x) {
+    const int i0 = (tile / (RET_CHUNK / 4)) * 4, tj = tile % (RET_CHUNK / 4);
+    float acc[4][4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[p][q] = 0.f;
+    for (int d = 0; d < a.dim; ++d) {
+      float q4[4], k4[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        q4[p] = qs[(i0 + p) * dimp + d];
+        k4[p] = ks[(tj + p * (RET_CHUNK / 4)) * dimp + d];
+      }
+#pragma unroll
+      for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(q4[p], k4[q], acc[p][q]);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int i = i0 + p, j = tj + q * (RET_CHUNK / 4);
+        pp[i * (RET_CHUNK + 1) + j] = (j <= i && i < len) ? acc[p][q] * powf(dec, (float)(i - j)) : 0.f;
+      }
   }
   __syncthreads();
-  const float* S = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
-  for (int e = tid; e < len * a.vdim; e += blockDim.x) {
-    const int i = e / a.vdim, y = e % a.vdim;
-    float cross = 0.f;
-    for (int d = 0; d < a.dim; ++d) cross = fmaf(qs[i * a.dim + d], S[d * a.vdim + y], cross);
-    float acc = cross * powf(dec, (float)(i + 1));
-    for (int j = 0; j <= i; ++j) acc = fmaf(pp[i * RET_CHUNK + j], vv[j * a.vdim + y], acc);
-    os[e] = acc;
+  const int tiles_y = vdimp >> 2, tiles_i = (len + 3) >> 2;
+  for (int tile = tid; tile < tiles_i * tiles_y; tile += blockDim.x) {
+    const int i0 = (tile / tiles_y) * 4, ty = tile % tiles_y;
+    float acc[4][4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[p][q] = 0.f;
+    for (int d = 0; d < a.dim; ++d) {
+      float q4[4], s4[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        q4[p] = qs[(i0 + p) * dimp + d];
+        const int y = ty + p * tiles_y;
+        s4[p] = stage_s ? Ss[d * vdimp + y] : (y < a.vdim ? S[d * a.vdim + y] : 0.f);
+      }
+#pragma unroll
+      for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(q4[p], s4[q], acc[p][q]);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float sc = powf(dec, (float)(i0 + p + 1));
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[p][q] *= sc;
+    }
+    const int jmax = min(i0 + 3, len - 1);
+    for (int j = 0; j <= jmax; ++j) {
+      float p4[4], v4[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        p4[p] = pp[(i0 + p) * (RET_CHUNK + 1) + j];
+        v4[p] = vv[j * vdimp + ty + p * tiles_y];
+      }
+#pragma unroll
+      for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(p4[p], v4[q], acc[p][q]);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) os[(i0 + p) * vdimp + ty + q * tiles_y] = acc[p][q];
   }
   __syncthreads();
   // one warp per row: root mean square over the head's vdim outputs
   const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
   for (int i = warp; i < len; i += nwarp) {
     float ss = 0.f;
-    for (int y = lane; y < a.vdim; y += 32) ss = fmaf(os[i * a.vdim + y], os[i * a.vdim + y], ss);
+    for (int y = lane; y < a.vdim; y += 32) ss = fmaf(os[i * vdimp + y], os[i * vdimp + y], ss);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) rr[i] = 1.0f / sqrtf(ss / (float)a.vdim + a.eps);
@@ -174,7 +271,7 @@ retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const i
   for (int e = tid; e < len * a.vdim; e += blockDim.x) {
     const int i = e / a.vdim, y = e % a.vdim;
     const float g = a.qkvg[(long long)(row0 + i) * a.ld + a.g_off + h * a.vdim + y];
-    const float v = os[e] * rr[i] * (g / (1.0f + expf(-g)));
+    const float v = os[i * vdimp + y] * rr[i] * (g / (1.0f + expf(-g)));
     const long long o = (long long)(row0 + i) * a.ldo + h * a.vdim + y;
     if (a.out_fp32) reinterpret_cast<float*>(a.out)[o] = v;
     else reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16(v);
@@ -182,7 +279,7 @@ retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const i
 }
 
 // decode: one new row per request.  Threads own state columns; with vdim < blockDim several thread groups split the dim rows.
-constexpr int RET_DEC_THREADS = 128;
+constexpr int RET_DEC_THREADS = 256;
 __global__ void __launch_bounds__(RET_DEC_THREADS)
 retention_decode_kernel(RetArgs a, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot) {
   extern __shared__ float dyn_smem[];
@@ -211,6 +308,7 @@ retention_decode_kernel(RetArgs a, const int* __restrict__ seq_row0, const int* 
     const int d0 = g * per, d1 = min(a.dim, d0 + per);
     for (int y = tid % a.vdim; y < a.vdim; y += blockDim.x) {
       float acc = 0.f;
+#pragma unroll 8
       for (int d = d0; d < d1; ++d) {
         const float old = fresh ? 0.f : st[(long long)d * a.vdim + y];
         const float S = fmaf(dec, old, ks[d] * vv[y]);
@@ -296,36 +394,34 @@ latent_prep_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int*
   }
 }
 
-// One warp per (row, head).  NR = ceil(kv_rank / 32) accumulators per lane.
+// One CTA per (row, head): its warps take every LAT_WARPS-th visible key with an online softmax of their own, then the partial
+// (maximum, denominator, weighted sum) triples are merged.  NR = ceil(kv_rank / 32) accumulators per lane.
 constexpr int LAT_WARPS = 4;
+constexpr int LAT_MAX_RANK = 1024;
 template <int NR>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, const float* __restrict__ q_abs,
                      long long ldqa, void* __restrict__ out, long long ldo, int out_fp32) {
-  const int item = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  __shared__ float s_acc[LAT_WARPS][LAT_MAX_RANK];
+  __shared__ float s_mx[LAT_WARPS], s_den[LAT_WARPS];
+  const int item = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (item >= R * a.heads) return;
   const int r = item / a.heads, h = item % a.heads;
   const int seq = row_seq[r], pos = row_pos[r];
   const float* qa = q_abs + (long long)r * ldqa + (long long)h * a.kv_rank;
   const float* qr = a.q + (long long)r * a.ldq + (long long)h * (a.dim + a.rot_dim) + a.dim;
-  float qv[NR], acc[NR];
+  float qv[NR], qrv[NR], acc[NR];
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int c = lane + 32 * i;
     qv[i] = c < a.kv_rank ? qa[c] : 0.f;
+    qrv[i] = c < a.rot_dim ? qr[c] : 0.f;      // rot_dim <= 32 * NR (checked by the host): lanes hold it strided as well
     acc[i] = 0.f;
-  }
-  // rotated part: rot_dim <= 32 * NR is required by the host; lanes hold it strided as well
-  float qrv[NR];
-#pragma unroll
-  for (int i = 0; i < NR; ++i) {
-    const int c = lane + 32 * i;
-    qrv[i] = c < a.rot_dim ? qr[c] : 0.f;
   }
   const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   float mx = -INFINITY, den = 0.f;
-  for (int j = lo; j <= pos; ++j) {
+  for (int j = lo + warp; j <= pos; j += LAT_WARPS) {
     const float* kv = lat_cache_row(a, seq, j);
     float cv[NR];
     float sc = 0.f;
@@ -340,24 +436,53 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
     for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
     sc *= a.scale;
     const float mn = fmaxf(mx, sc);
-    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the first key
+    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the warp's first key
     const float p = expf(sc - mn);
     den = den * corr + p;
 #pragma unroll
     for (int i = 0; i < NR; ++i) acc[i] = fmaf(p, cv[i], acc[i] * corr);
     mx = mn;
   }
-  const float inv = 1.0f / den;
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int c = lane + 32 * i;
-    if (c < a.kv_rank) {
-      const long long o = (long long)r * ldo + (long long)h * a.kv_rank + c;
-      if (out_fp32) reinterpret_cast<float*>(out)[o] = acc[i] * inv;
-      else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16(acc[i] * inv);
-    }
+    if (c < a.kv_rank) s_acc[warp][c] = acc[i];
+  }
+  if (lane == 0) {
+    s_mx[warp] = mx;
+    s_den[warp] = den;
+  }
+  __syncthreads();
+  float top = s_mx[0];
+#pragma unroll
+  for (int w = 1; w < LAT_WARPS; ++w) top = fmaxf(top, s_mx[w]);
+  float f[LAT_WARPS], total = 0.f;
+#pragma unroll
+  for (int w = 0; w < LAT_WARPS; ++w) {
+    f[w] = s_den[w] > 0.f ? expf(s_mx[w] - top) : 0.f;      // a warp without keys contributes nothing
+    total = fmaf(s_den[w], f[w], total);
+  }
+  const float inv = 1.0f / total;
+  for (int c = threadIdx.x; c < a.kv_rank; c += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < LAT_WARPS; ++w) v = fmaf(s_acc[w][c], f[w], v);
+    const long long o = (long long)r * ldo + (long long)h * a.kv_rank + c;
+    if (out_fp32) reinterpret_cast<float*>(out)[o] = v * inv;
+    else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16(v * inv);
   }
 }
+
+// raise a kernel's dynamic shared-memory limit only when a launch needs more than any launch before it (no runtime call on the
+// steady path, so the steady path can be captured into a CUDA graph)
+template <typename K>
+static cudaError_t ensure_smem(K kern, size_t bytes, size_t& have) {
+  if (bytes <= have) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) have = bytes;
+  return e;
+}
+static size_t g_smem_chunk_state = 48 * 1024, g_smem_chunk_out = 48 * 1024, g_smem_ret_decode = 48 * 1024;
 
 static int fill_ret(RetArgs& a, const lp_retention_desc* d) {
   LP_REQUIRE(d != nullptr && d->qkvg != nullptr && d->decay != nullptr && d->state != nullptr && d->out != nullptr,
@@ -411,16 +536,20 @@ extern "C" int lp_retention_prefill(const lp_retention_desc* d, int n_seqs, int 
   LP_REQUIRE(ws != nullptr && ws_bytes >= lp_retention_workspace_bytes(n_chunks, d->heads, d->dim, d->vdim),
              "lp_retention_prefill: workspace too small");
   float* w = reinterpret_cast<float*>(ws);
-  const size_t smem1 = (size_t)RET_CHUNK * (d->dim + d->vdim) * sizeof(float);
-  const size_t smem3 = ((size_t)RET_CHUNK * (2 * d->dim + 2 * d->vdim) + RET_CHUNK * RET_CHUNK + RET_CHUNK) * sizeof(float);
+  const size_t dimp = ((d->dim + 3) & ~3) + 1, vdimp = (d->vdim + 3) & ~3;
+  const size_t smem1 = (size_t)RET_CHUNK * (dimp + vdimp) * sizeof(float);
+  size_t smem3 = ((size_t)RET_CHUNK * (2 * dimp + 2 * vdimp) + RET_CHUNK * (RET_CHUNK + 1) + RET_CHUNK) * sizeof(float);
   LP_REQUIRE(smem3 <= 200 * 1024, "lp_retention_prefill: dim=%d vdim=%d do not fit the chunk kernel's shared memory", d->dim, d->vdim);
-  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
-  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
+  const int stage_s = smem3 + (size_t)d->dim * vdimp * sizeof(float) <= 200 * 1024;      // the chunk's start state next to the operands
+  if (stage_s) smem3 += (size_t)d->dim * vdimp * sizeof(float);
+  LP_CHECK_CUDA(ensure_smem(retention_chunk_state_kernel, smem1, g_smem_chunk_state));
+  LP_CHECK_CUDA(ensure_smem(retention_chunk_out_kernel, smem3, g_smem_chunk_out));
   retention_chunk_state_kernel<<<dim3(n_chunks, d->heads), 128, smem1, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
   LP_CHECK_CUDA(cudaGetLastError());
   retention_scan_kernel<<<dim3(n_seqs, d->heads), 256, 0, stream>>>(a, seq_chunk0, chunk_len, seq_pos0, seq_slot, w);
   LP_CHECK_CUDA(cudaGetLastError());
-  retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), 128, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
+  retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), 128, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w,
+                                                                                stage_s);
   LP_CHECK_CUDA(cudaGetLastError());
   note_launch(3);
   return 0;
@@ -435,7 +564,7 @@ extern "C" int lp_retention_decode(const lp_retention_desc* d, int n_seqs, const
   const int groups = d->vdim >= RET_DEC_THREADS ? 1 : RET_DEC_THREADS / d->vdim;
   const size_t smem = ((size_t)2 * d->dim + 2 * d->vdim + (size_t)groups * d->vdim) * sizeof(float);
   LP_REQUIRE(smem <= 200 * 1024, "lp_retention_decode: dim=%d vdim=%d do not fit shared memory", d->dim, d->vdim);
-  LP_CHECK_CUDA(cudaFuncSetAttribute(retention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LP_CHECK_CUDA(ensure_smem(retention_decode_kernel, smem, g_smem_ret_decode));
   retention_decode_kernel<<<dim3(n_seqs, d->heads), RET_DEC_THREADS, smem, stream>>>(a, seq_row0, seq_pos0, seq_slot);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
@@ -461,10 +590,10 @@ extern "C" int lp_latent_attend(const lp_latent_desc* d, int R, const int* row_s
   if (int rc = fill_lat(a, d)) return rc;
   LP_REQUIRE(q_abs != nullptr && out != nullptr && row_seq != nullptr && row_pos != nullptr, "lp_latent_attend: null operand");
   LP_REQUIRE(d->rot_dim <= d->kv_rank || d->rot_dim <= 32, "lp_latent_attend: rot_dim=%d must not exceed kv_rank=%d", d->rot_dim, d->kv_rank);
-  LP_REQUIRE(d->kv_rank <= 1024, "lp_latent_attend: kv_rank=%d > 1024 is not instantiated", d->kv_rank);
+  LP_REQUIRE(d->kv_rank <= LAT_MAX_RANK, "lp_latent_attend: kv_rank=%d > %d is not instantiated", d->kv_rank, LAT_MAX_RANK);
   if (R <= 0) return 0;
   const int nr = (d->kv_rank + 31) / 32;
-  const unsigned grid = (unsigned)(((long long)R * d->heads + LAT_WARPS - 1) / LAT_WARPS);
+  const unsigned grid = (unsigned)((long long)R * d->heads);
   if (nr <= 2) latent_attend_kernel<2><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
   else if (nr <= 4) latent_attend_kernel<4><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
   else if (nr <= 8) latent_attend_kernel<8><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);

@@ -28,6 +28,7 @@ from .seqcache import SequenceCache
 
 F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
 TENSOR_CORE_MIN_ROWS = 128
+PAGE_TABLE_STEP = 16           # decode batches round their page-table width up to a multiple of this
 
 
 # ---------------------------------------------------------------------------------------------------------------- configuration
@@ -212,7 +213,9 @@ class StepEntry:
 class _Batch:
     """Index tables of one step, built on the host and copied to the device in one transfer."""
 
-    def __init__(self, eng: "SeqLMEngine", entries: Sequence[StepEntry]):
+    def __init__(self, eng: "SeqLMEngine", entries: Sequence[StepEntry], static: Optional[Dict] = None):
+        """static: {(n, table width): device int32 buffer} — a decode batch whose layout has been seen before is copied into the same
+        device buffer again, so that a captured graph of the step finds its tables where they were."""
         cache = eng.cache
         seqs = []
         for e in entries:
@@ -237,6 +240,8 @@ class _Batch:
         row_seq = np.repeat(np.arange(n, dtype=np.int32), lens)
         row_pos = np.concatenate([np.arange(p, p + ln, dtype=np.int32) for p, ln in zip(pos0, lens)])
         max_pages = max([len(s.pages) for s in seqs] + [1])
+        if self.decode:
+            max_pages = -(-max_pages // PAGE_TABLE_STEP) * PAGE_TABLE_STEP      # the width is a launch argument: change it rarely
         table = np.full((n, max_pages), -1, np.int32)
         for i, s in enumerate(seqs):
             table[i, : len(s.pages)] = s.pages
@@ -256,17 +261,29 @@ class _Batch:
                 raise ValueError(f"request {e.key!r}: a wanted index is outside its tokens")
         self.n_want = len(want)
         parts = [tokens.astype(np.int32), row_seq, row_pos, row0, pos0, slot, table.reshape(-1), np.asarray(c_seq, np.int32),
-                 np.asarray(c_row0, np.int32), np.asarray(c_len, np.int32), np.asarray(seq_c0, np.int32), np.asarray(want, np.int32)]
-        flat = torch.from_numpy(np.concatenate(parts).astype(np.int32))
+                 np.asarray(c_row0, np.int32), np.asarray(c_len, np.int32), np.asarray(seq_c0, np.int32)]
+        tables = torch.from_numpy(np.concatenate(parts).astype(np.int32))
+        want_t = torch.from_numpy(np.asarray(want, np.int32))
+        self.layout = (n, max_pages) if self.decode else None      # fixes the size of every table of a decode batch
         if eng.device.type == "cuda":
-            flat = flat.pin_memory().to(eng.device, non_blocking=True)
+            host = tables.pin_memory()
+            if static is not None and self.decode:
+                tables = static.get(self.layout)
+                if tables is None:
+                    tables = static[self.layout] = torch.empty(len(host), dtype=I32, device=eng.device)
+                tables.copy_(host, non_blocking=True)
+            else:
+                tables = host.to(eng.device, non_blocking=True)
+            if len(want):
+                want_t = want_t.pin_memory().to(eng.device, non_blocking=True)
         views, o = [], 0
         for p in parts:
-            views.append(flat[o:o + len(p)])
+            views.append(tables[o:o + len(p)])
             o += len(p)
         (self.tokens, self.row_seq, self.row_pos, self.seq_row0, self.seq_pos0, self.seq_slot, self.page_table, self.chunk_seq,
-         self.chunk_row0, self.chunk_len, self.seq_chunk0, self.want_rows) = views
-        self._flat = flat
+         self.chunk_row0, self.chunk_len, self.seq_chunk0) = views
+        self.want_rows = want_t
+        self._tables = tables
 
 
 # ---------------------------------------------------------------------------------------------------------------- engine
@@ -298,6 +315,13 @@ class SeqLMEngine:
         # large bf16 products of the serving precision go to the tcgen05 GEMM when the library has it (the native ones do)
         self.tensor_core_rows = TENSOR_CORE_MIN_ROWS if dtype == "bfloat16" and hasattr(self.L, "lp_gemm_bf16") else None
         self.tap: Optional[Callable[[int, torch.Tensor], None]] = None   # called with (layer, residual stream) after every layer
+        # decode steps are launch-bound: a batch layout (requests, page-table width) that comes back is captured into a CUDA graph on
+        # its second appearance and replayed from then on; only the index tables change between replays (LEOPARD_DECODE_GRAPH=0: off)
+        import os
+        self.use_graphs = self.device.type == "cuda" and os.environ.get("LEOPARD_DECODE_GRAPH", "1") != "0"
+        self._static_tables: Dict = {}
+        self._graphs: Dict = {}
+        self._seen: Dict = {}
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -427,16 +451,32 @@ class SeqLMEngine:
         self._check(rc, "lp_moe_align")
         rows = tiles * self.tile_rows
         h1 = self._empty((rows, f.expert_ff), self.act)
-        w_gu, w_dn = lw["w_gu"], lw["w_edown"]
-        d1 = _lib.LinearDesc(A=_lib.ptr(h), lda=h.stride(0), a_batch=0, a_fp32=int(h.dtype == F32), W=_lib.ptr(w_gu), ldw=w_gu.stride(1),
-                             w_batch=w_gu.stride(0), C=_lib.ptr(h1), ldc=h1.stride(0), c_batch=0, c_fp32=int(h1.dtype == F32), M=rows,
-                             N=2 * f.expert_ff, K=D, batch=1, epi=_lib.EPI_SILU_GATE, epi_a=0.0, epi_b=0.0)
-        self._check(L.lp_linear_grouped(C.byref(d1), _lib.ptr(tile_group), tiles, _lib.ptr(sorted_token), st), "lp_linear_grouped")
         y = self._empty((rows, D), F32)
-        d2 = _lib.LinearDesc(A=_lib.ptr(h1), lda=h1.stride(0), a_batch=0, a_fp32=int(h1.dtype == F32), W=_lib.ptr(w_dn), ldw=w_dn.stride(1),
-                             w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=rows, N=D, K=f.expert_ff,
-                             batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
-        self._check(L.lp_linear_grouped(C.byref(d2), _lib.ptr(tile_group), tiles, None, st), "lp_linear_grouped")
+        w_gu, w_dn = lw["w_gu"], lw["w_edown"]
+        if self.tensor_core_rows is not None and n_pairs >= f.experts * self.tensor_core_rows and h.dtype == BF16:
+            # prefill in the serving precision: enough rows per expert to fill tensor-core tiles.  The segment bounds come to the host
+            # (one small device -> host copy), the rows are gathered into expert order and every expert runs two tcgen05 GEMMs.
+            groups = tile_group.cpu().tolist()
+            a_sorted = h.index_select(0, sorted_token.clamp_min(0).long())
+            t0 = 0
+            while t0 < tiles:
+                e, t1 = groups[t0], t0 + 1
+                while t1 < tiles and groups[t1] == e:
+                    t1 += 1
+                if e >= 0:
+                    r0, r1 = t0 * self.tile_rows, t1 * self.tile_rows
+                    self.linear(a_sorted[r0:r1], w_gu[e], self.act, _lib.EPI_SILU_GATE, out=h1[r0:r1])
+                    self.linear(h1[r0:r1], w_dn[e], F32, out=y[r0:r1])
+                t0 = t1
+        else:
+            d1 = _lib.LinearDesc(A=_lib.ptr(h), lda=h.stride(0), a_batch=0, a_fp32=int(h.dtype == F32), W=_lib.ptr(w_gu), ldw=w_gu.stride(1),
+                                 w_batch=w_gu.stride(0), C=_lib.ptr(h1), ldc=h1.stride(0), c_batch=0, c_fp32=int(h1.dtype == F32), M=rows,
+                                 N=2 * f.expert_ff, K=D, batch=1, epi=_lib.EPI_SILU_GATE, epi_a=0.0, epi_b=0.0)
+            self._check(L.lp_linear_grouped(C.byref(d1), _lib.ptr(tile_group), tiles, _lib.ptr(sorted_token), st), "lp_linear_grouped")
+            d2 = _lib.LinearDesc(A=_lib.ptr(h1), lda=h1.stride(0), a_batch=0, a_fp32=int(h1.dtype == F32), W=_lib.ptr(w_dn),
+                                 ldw=w_dn.stride(1), w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=rows,
+                                 N=D, K=f.expert_ff, batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
+            self._check(L.lp_linear_grouped(C.byref(d2), _lib.ptr(tile_group), tiles, None, st), "lp_linear_grouped")
         shared = None
         if f.shared_ff:
             s1 = self.linear(h, lw["ws_gu"], self.act, _lib.EPI_SILU_GATE)
@@ -456,7 +496,38 @@ class SeqLMEngine:
             return None
         if len({e.key for e in entries}) != len(entries):
             raise ValueError("a request appears twice in one step")
-        b = _Batch(self, entries)
+        b = _Batch(self, entries, self._static_tables if self.use_graphs else None)
+        if b.decode and self.use_graphs and self.tap is None:
+            logits = self._decode_replay(b)
+        else:
+            logits = self._forward(b, b.want_rows if b.n_want else None)
+        for s, ln in zip(b.seqs, b.lens):
+            self.cache.advance(s, ln)
+        return logits
+
+    def _decode_replay(self, b: _Batch) -> Optional[torch.Tensor]:
+        """One-token-per-request steps: eager the first time a layout is seen, captured the second time, replayed afterwards.  The
+        graph computes the logits of every row; the wanted ones are picked afterwards."""
+        key = (b.layout, self.cache.generation)
+        g = self._graphs.get(key)
+        if g is None:
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if self._seen[key] < 2:
+                return self._forward(b, b.want_rows if b.n_want else None)
+            for old in [k for k in self._graphs if k[1] != self.cache.generation]:
+                del self._graphs[old]                      # pools were reallocated: those graphs point at freed memory
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                out = self._forward(b, "all")
+            g = self._graphs[key] = (graph, out)
+        g[0].replay()
+        if b.n_want == 0:
+            return None
+        return g[1].index_select(0, b.want_rows.long()) if b.n_want != b.R else g[1].clone()
+
+    def _forward(self, b: _Batch, want) -> Optional[torch.Tensor]:
+        """embedding -> layers -> (final norm, head) over the rows `want` (a device index tensor, "all", or None)"""
         cfg, D = self.cfg, self.cfg.width
         x = self._empty((b.R, D), F32)
         rc = self.L.lp_embed_rows_f32(_lib.ptr(b.tokens), b.R, _lib.ptr(self.w.embed), self.w.embed.stride(0), cfg.vocab, _lib.ptr(x),
@@ -475,11 +546,9 @@ class SeqLMEngine:
                 self.norm(y, lw["norm2b"], accum=x)
             if self.tap is not None:
                 self.tap(li, x)
-        for s, ln in zip(b.seqs, b.lens):
-            self.cache.advance(s, ln)
-        if b.n_want == 0:
+        if want is None:
             return None
-        rows = x if (b.n_want == b.R and b.R == 1) else x.index_select(0, b.want_rows.long())
+        rows = x if isinstance(want, str) else x.index_select(0, want.long())
         hn = self.norm(rows, self.w.final_gain, self.act)
         return self.linear(hn, self.w.head, F32)
 

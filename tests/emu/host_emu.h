@@ -54,6 +54,7 @@ inline long long clock64() { return 0; }
 inline void __trap() { std::abort(); }
 template <typename T> inline T __ldcg(const T* p) { return *p; }
 inline float __bfloat162float(__nv_bfloat16 v) { return (float)v; }
+inline float __uint_as_float(unsigned u) { float f; std::memcpy(&f, &u, 4); return f; }
 inline __nv_bfloat16 __ushort_as_bfloat16(unsigned short u) { __nv_bfloat16 r; r.bits = u; return r; }
 #define __align__(n) alignas(n)
 #define LP_WATCHDOG_CYCLES (1LL << 62)
