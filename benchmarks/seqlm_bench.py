@@ -165,6 +165,8 @@ def bench_size(name, s, dev, steps, warmup, peaks, prompt):
     keys = sum(min(p + 1, s["window"]) for p in range(R))
     lat_flops = H * keys * (2.0 * (s["kv_rank"] + 64) + 2.0 * s["kv_rank"])
     moe_flops = 2 * (R * s["top"] * 2.0 * D * s["expert_ff"] * 3)
+    if "lp_linear_grouped" not in kp:         # the experts ran as tcgen05 GEMMs over their sorted row segments
+        flops_gemm += moe_flops
     def rate(key, flops):
         return round(flops / (kp[key]["ms"] * 1e-3) / 1e12, 2) if key in kp and kp[key]["ms"] > 0 else None
     out["prefill_kernels"] = kp
@@ -191,10 +193,10 @@ def bench_size(name, s, dev, steps, warmup, peaks, prompt):
         ms = _time(decode, steps, warmup)
         d = {"ms_per_step": round(ms, 3), "tokens_per_s": round(batch / ms * 1e3, 1)}
         if batch in (1, 8):
-            eng.L = TimedLib(plain)
+            eng.L, eng.use_graphs = TimedLib(plain), False      # the breakdown needs the launches one by one
             decode()
             kd = eng.L.collect()
-            eng.L = plain
+            eng.L, eng.use_graphs = plain, True
             d["kernels"] = kd
             # weight bytes the dense products stream once per step (rows kernel): everything but the experts, plus the head
             wbytes = 0

@@ -585,6 +585,7 @@ int lp_parity_softmax(float* scores, long long ld, int Tq, int Tk, float scale, 
 enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2 };
 enum lp_rot_layout { LP_ROT_HALF = 0, LP_ROT_INTERLEAVED = 1 };
 #define LP_RETENTION_CHUNK 32
+#define LP_LATENT_SPLIT_ROWS 16   /* lp_latent_attend: up to this many rows a CTA per (row, head) splits the keys over its warps */
 
 /* C[M, N'] = epi(A[M, K] W[N, K]^T), `batch` problems `*_batch` elements apart.  A: fp32 (a_fp32) or bf16; W: bf16; C: fp32 (c_fp32) or
  * bf16.  epi XIELU: a z^2 + z/2 (z > 0), b (exp(z) - 1 - z) + z/2 (z <= 0) with a = epi_a, b = epi_b.  epi SILU_GATE: W = [gate rows;
@@ -601,6 +602,8 @@ int lp_linear(const lp_linear_desc* desc, void* stream);
  * tile is skipped); a_rows[row] (optional) = the A row to read for that row of the sorted space (< 0: zeros). */
 int lp_linear_grouped(const lp_linear_desc* desc, const int* tile_group, int n_tiles, const int* a_rows, void* stream);
 int lp_linear_tile_rows(void);
+/* n_pairs one-row problems: problem z = A row z / a_div times the weight of group pair_group[z] -> C row z (weight-streaming kernel) */
+int lp_linear_pairs(const lp_linear_desc* desc, const int* pair_group, int a_div, int n_pairs, void* stream);
 
 int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float* out, long long ldo, int D, void* stream);
 /* y = x / sqrt(mean(x^2) + eps) * gain_scalar (* gain_vec[c]); written to `out` (fp32 or bf16) or added to `accum` (fp32) */

@@ -191,6 +191,7 @@ _SIGS = {
     "lp_linear": (_i, [C.POINTER(LinearDesc), _vp]),
     "lp_linear_grouped": (_i, [C.POINTER(LinearDesc), _vp, _i, _vp, _vp]),
     "lp_linear_tile_rows": (_i, []),
+    "lp_linear_pairs": (_i, [C.POINTER(LinearDesc), _vp, _i, _i, _vp]),
     "lp_embed_rows_f32": (_i, [_vp, _i, _vp, _ll, _i, _vp, _ll, _i, _vp]),
     "lp_rmsnorm_f32": (_i, [_vp, _ll, _i, _i, _f, _vp, _f, _vp, _ll, _i, _vp, _ll, _vp]),
     "lp_glu_f32": (_i, [_vp, _ll, _i, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp]),
@@ -244,7 +245,7 @@ def lib():
 # They need none of the tcgen05 translation units, so a model that uses only them can run from a library of its own that compiles in
 # seconds (build.build_native("stream32")); the full library contains the same symbols and is preferred when it is already built.
 STREAM32_LIB_PATH = PKG / "lib" / "libleopard_stream32.so"
-STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_linear", "lp_linear_grouped", "lp_linear_tile_rows",
+STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_linear", "lp_linear_grouped", "lp_linear_tile_rows", "lp_linear_pairs",
                     "lp_embed_rows_f32", "lp_rmsnorm_f32", "lp_glu_f32", "lp_retention_workspace_bytes", "lp_retention_prefill",
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
                     "lp_moe_combine")

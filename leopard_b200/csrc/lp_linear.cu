@@ -29,6 +29,8 @@ struct LinArgs {
   int epi; float e0, e1;  // lp_linear_epi and its two constants
   const int* a_rows;      // grouped: source row of each sorted row, or NULL
   const int* tile_group;  // grouped: group of each row tile, or NULL
+  const int* z_group;     // pairs (rows kernel): weight group of problem z, or NULL; problem z reads A row z / a_div and writes C row z
+  int a_div;
 };
 
 __device__ __forceinline__ float lin_load(const float* p) { return *p; }
@@ -140,9 +142,11 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
   const int z = blockIdx.z;
   const int n_out = GATED ? a.N / 2 : a.N;
   if (n >= n_out) return;
-  const AT* A = reinterpret_cast<const AT*>(a.A) + (long long)z * a.a_batch;
-  const bf16* W = a.W + (long long)z * a.w_batch;
-  CT* C = reinterpret_cast<CT*>(a.C) + (long long)z * a.c_batch;
+  const bool pairs = a.z_group != nullptr;
+  const int M = pairs ? 1 : a.M;
+  const AT* A = reinterpret_cast<const AT*>(a.A) + (pairs ? (long long)(z / a.a_div) * a.lda : (long long)z * a.a_batch);
+  const bf16* W = a.W + (long long)(pairs ? a.z_group[z] : z) * a.w_batch;
+  CT* C = reinterpret_cast<CT*>(a.C) + (pairs ? (long long)z * a.ldc : (long long)z * a.c_batch);
   const bf16* w1 = W + (long long)n * a.ldw;
   const bf16* w2 = W + (long long)(n + n_out) * a.ldw;
   float acc[ROWS_MAX], acc2[GATED ? ROWS_MAX : 1];
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
       bf16x8_to_f32(u2, f2);
 #pragma unroll
       for (int m = 0; m < ROWS_MAX; ++m) {
-        if (m < a.M) {
+        if (m < M) {
           const AT* ar = A + (long long)m * a.lda + k;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
       const float f2 = GATED ? __bfloat162float(w2[k]) : 0.f;
 #pragma unroll
       for (int m = 0; m < ROWS_MAX; ++m) {
-        if (m < a.M) {
+        if (m < M) {
           const float x = lin_load(A + (long long)m * a.lda + k);
           acc[m] = fmaf(x, f1, acc[m]);
           if (GATED) acc2[m] = fmaf(x, f2, acc2[m]);
@@ -189,7 +193,7 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
   }
 #pragma unroll
   for (int m = 0; m < ROWS_MAX; ++m) {
-    if (m < a.M) {
+    if (m < M) {
       float s = acc[m], s2 = GATED ? acc2[m] : 0.f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -251,8 +255,28 @@ extern "C" int lp_linear(const lp_linear_desc* d, void* stream_) {
   a.C = d->C; a.ldc = d->ldc; a.c_batch = d->c_batch;
   a.M = d->M; a.N = d->N; a.K = d->K;
   a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
-  a.a_rows = nullptr; a.tile_group = nullptr;
+  a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = nullptr; a.a_div = 1;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, d->batch, (d->M + LIN_BM - 1) / LIN_BM, true, stream);
+}
+
+// n_pairs one-row problems on the weight-streaming kernel: problem z multiplies A row z / a_div by the weight of group pair_group[z]
+// (w_batch elements apart) into C row z — the expert products of a decode step, where every (token, choice) pair has its own weight.
+extern "C" int lp_linear_pairs(const lp_linear_desc* d, const int* pair_group, int a_div, int n_pairs, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr && pair_group != nullptr, "lp_linear_pairs: null operand");
+  LP_REQUIRE(d->N > 0 && d->K > 0 && a_div >= 1 && n_pairs >= 0 && n_pairs <= 65535, "lp_linear_pairs: bad problem N=%d K=%d pairs=%d", d->N,
+             d->K, n_pairs);
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_SILU_GATE, "lp_linear_pairs: bad epilogue %d", d->epi);
+  LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear_pairs: the gated epilogue needs an even N");
+  if (n_pairs == 0) return 0;
+  LinArgs a;
+  a.A = d->A; a.lda = d->lda; a.a_batch = 0;
+  a.W = reinterpret_cast<const bf16*>(d->W); a.ldw = d->ldw; a.w_batch = d->w_batch;
+  a.C = d->C; a.ldc = d->ldc; a.c_batch = 0;
+  a.M = 1; a.N = d->N; a.K = d->K;
+  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
+  a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = pair_group; a.a_div = a_div;
+  return dispatch_linear(a, d->a_fp32, d->c_fp32, n_pairs, 1, true, stream);
 }
 
 extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group, int n_tiles, const int* a_rows, void* stream_) {
@@ -269,7 +293,7 @@ extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group,
   a.C = d->C; a.ldc = d->ldc; a.c_batch = 0;
   a.M = n_tiles * LIN_BM; a.N = d->N; a.K = d->K;
   a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
-  a.a_rows = a_rows; a.tile_group = tile_group;
+  a.a_rows = a_rows; a.tile_group = tile_group; a.z_group = nullptr; a.a_div = 1;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, 1, n_tiles, false, stream);
 }
 

@@ -121,26 +121,38 @@ retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const
   }
 }
 
-// (2) per (request, head): ws[chunk] <- state at the chunk's start; the state after the last chunk goes to the slot
-__global__ void __launch_bounds__(256)
+// (2) one thread per state element of a (request, head): ws[chunk] <- state at the chunk's start; the state after the last chunk goes
+// to the slot.  The chunks' own contributions are loaded eight at a time (independent loads) ahead of the dependent multiply-adds.
+constexpr int SCAN_THREADS = 256, SCAN_BATCH = 8;
+__global__ void __launch_bounds__(SCAN_THREADS)
 retention_scan_kernel(RetArgs a, const int* __restrict__ seq_chunk0, const int* __restrict__ chunk_len, const int* __restrict__ seq_pos0,
                       const int* __restrict__ seq_slot, float* __restrict__ ws) {
   const int s = blockIdx.x, h = blockIdx.y;
+  const long long hs = (long long)a.dim * a.vdim;
+  const long long i = (long long)blockIdx.z * SCAN_THREADS + threadIdx.x;
+  if (i >= hs) return;
   const int c0 = seq_chunk0[s], c1 = seq_chunk0[s + 1];
   const float dec = a.decay[h];
-  const long long hs = (long long)a.dim * a.vdim;
-  float* st = a.state + (long long)seq_slot[s] * a.slot_stride + h * hs;
-  const bool fresh = seq_pos0[s] == 0;
-  for (int i = threadIdx.x; i < hs; i += blockDim.x) {
-    float S = fresh ? 0.f : st[i];
-    for (int c = c0; c < c1; ++c) {
-      float* u = ws + ((long long)c * a.heads + h) * hs + i;
-      const float own = *u;
-      *u = S;
-      S = fmaf(powf(dec, (float)chunk_len[c]), S, own);
+  const float dec_full = powf(dec, (float)RET_CHUNK);
+  float* st = a.state + (long long)seq_slot[s] * a.slot_stride + h * hs + i;
+  float S = seq_pos0[s] == 0 ? 0.f : *st;
+  const long long stride = (long long)a.heads * hs;
+  float* u = ws + ((long long)c0 * a.heads + h) * hs + i;
+  for (int c = c0; c < c1; c += SCAN_BATCH) {
+    float own[SCAN_BATCH];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) own[k] = c + k < c1 ? u[k * stride] : 0.f;
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (c + k < c1) {
+        const int len = chunk_len[c + k];
+        u[k * stride] = S;
+        S = fmaf(len == RET_CHUNK ? dec_full : powf(dec, (float)len), S, own[k]);
+      }
     }
-    st[i] = S;
+    u += SCAN_BATCH * stride;
   }
+  *st = S;
 }
 
 // (3) o_i = decay^(i+1) q_i^T S_start + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j; then o / rms(o) * silu(g).  The chunk's start state is
@@ -473,6 +485,65 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
   }
 }
 
+// Many rows (prompts): one CTA per row, one warp per head (up to LAT_ROW_HEADS heads per CTA), every warp walks all visible keys.
+// The heads of a row read the same cache rows at about the same time, so the cache traffic of a row is paid once per CTA (L1), and
+// neighbouring rows overlap in all but one key (L2).
+constexpr int LAT_ROW_HEADS = 16;
+template <int NR>
+__global__ void __launch_bounds__(LAT_ROW_HEADS * 32)
+latent_attend_rows_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, const float* __restrict__ q_abs,
+                          long long ldqa, void* __restrict__ out, long long ldo, int out_fp32) {
+  const int r = blockIdx.x;
+  const int h = blockIdx.y * LAT_ROW_HEADS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= R || h >= a.heads) return;
+  const int seq = row_seq[r], pos = row_pos[r];
+  const float* qa = q_abs + (long long)r * ldqa + (long long)h * a.kv_rank;
+  const float* qr = a.q + (long long)r * a.ldq + (long long)h * (a.dim + a.rot_dim) + a.dim;
+  float qv[NR], qrv[NR], acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int c = lane + 32 * i;
+    qv[i] = c < a.kv_rank ? qa[c] : 0.f;
+    qrv[i] = c < a.rot_dim ? qr[c] : 0.f;
+    acc[i] = 0.f;
+  }
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  float mx = -INFINITY, den = 0.f;
+  for (int j = lo; j <= pos; ++j) {
+    const float* kv = lat_cache_row(a, seq, j);
+    float cv[NR];
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int c = lane + 32 * i;
+      cv[i] = c < a.kv_rank ? kv[c] : 0.f;
+      sc = fmaf(qv[i], cv[i], sc);
+      if (c < a.rot_dim) sc = fmaf(qrv[i], kv[a.kv_rank + c], sc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+    sc *= a.scale;
+    const float mn = fmaxf(mx, sc);
+    const float corr = expf(mx - mn);
+    const float p = expf(sc - mn);
+    den = den * corr + p;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p, cv[i], acc[i] * corr);
+    mx = mn;
+  }
+  const float inv = 1.0f / den;
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int c = lane + 32 * i;
+    if (c < a.kv_rank) {
+      const long long o = (long long)r * ldo + (long long)h * a.kv_rank + c;
+      if (out_fp32) reinterpret_cast<float*>(out)[o] = acc[i] * inv;
+      else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16(acc[i] * inv);
+    }
+  }
+}
+
 // raise a kernel's dynamic shared-memory limit only when a launch needs more than any launch before it (no runtime call on the
 // steady path, so the steady path can be captured into a CUDA graph)
 template <typename K>
@@ -546,7 +617,8 @@ extern "C" int lp_retention_prefill(const lp_retention_desc* d, int n_seqs, int 
   LP_CHECK_CUDA(ensure_smem(retention_chunk_out_kernel, smem3, g_smem_chunk_out));
   retention_chunk_state_kernel<<<dim3(n_chunks, d->heads), 128, smem1, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
   LP_CHECK_CUDA(cudaGetLastError());
-  retention_scan_kernel<<<dim3(n_seqs, d->heads), 256, 0, stream>>>(a, seq_chunk0, chunk_len, seq_pos0, seq_slot, w);
+  retention_scan_kernel<<<dim3(n_seqs, d->heads, (d->dim * d->vdim + SCAN_THREADS - 1) / SCAN_THREADS), SCAN_THREADS, 0, stream>>>(
+      a, seq_chunk0, chunk_len, seq_pos0, seq_slot, w);
   LP_CHECK_CUDA(cudaGetLastError());
   retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), 128, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w,
                                                                                 stage_s);
@@ -593,12 +665,22 @@ extern "C" int lp_latent_attend(const lp_latent_desc* d, int R, const int* row_s
   LP_REQUIRE(d->kv_rank <= LAT_MAX_RANK, "lp_latent_attend: kv_rank=%d > %d is not instantiated", d->kv_rank, LAT_MAX_RANK);
   if (R <= 0) return 0;
   const int nr = (d->kv_rank + 31) / 32;
-  const unsigned grid = (unsigned)((long long)R * d->heads);
-  if (nr <= 2) latent_attend_kernel<2><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
-  else if (nr <= 4) latent_attend_kernel<4><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
-  else if (nr <= 8) latent_attend_kernel<8><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
-  else if (nr <= 16) latent_attend_kernel<16><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
-  else latent_attend_kernel<32><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  if (R > LP_LATENT_SPLIT_ROWS) {      // prompts: a CTA per row, a warp per head
+    const dim3 grid(R, (d->heads + LAT_ROW_HEADS - 1) / LAT_ROW_HEADS);
+    const int threads = (d->heads < LAT_ROW_HEADS ? d->heads : LAT_ROW_HEADS) * 32;
+    if (nr <= 2) latent_attend_rows_kernel<2><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 4) latent_attend_rows_kernel<4><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 8) latent_attend_rows_kernel<8><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 16) latent_attend_rows_kernel<16><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else latent_attend_rows_kernel<32><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  } else {                             // few rows (decoding): a CTA per (row, head), its warps split the keys
+    const unsigned grid = (unsigned)((long long)R * d->heads);
+    if (nr <= 2) latent_attend_kernel<2><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 4) latent_attend_kernel<4><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 8) latent_attend_kernel<8><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else if (nr <= 16) latent_attend_kernel<16><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+    else latent_attend_kernel<32><<<grid, LAT_WARPS * 32, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);
+  }
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -28,6 +28,7 @@ from .seqcache import SequenceCache
 
 F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
 TENSOR_CORE_MIN_ROWS = 128
+MOE_PAIRS_MAX = 64             # up to this many (token, choice) pairs the experts run as one-row weight-streaming problems
 PAGE_TABLE_STEP = 16           # decode batches round their page-table width up to a multiple of this
 
 
@@ -442,6 +443,20 @@ class SeqLMEngine:
                             _lib.ptr(lw["w_sg"]) if f.shared_ff else None, _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(gate), st)
         self._check(rc, "lp_moe_route")
         n_pairs = T * f.top
+        if n_pairs <= MOE_PAIRS_MAX:
+            # few (token, choice) pairs (decoding): no sorting — every pair streams its expert's weights once, pair z = row z
+            w_gu, w_dn = lw["w_gu"], lw["w_edown"]
+            h1 = self._empty((n_pairs, f.expert_ff), self.act)
+            d1 = _lib.LinearDesc(A=_lib.ptr(h), lda=h.stride(0), a_batch=0, a_fp32=int(h.dtype == F32), W=_lib.ptr(w_gu), ldw=w_gu.stride(1),
+                                 w_batch=w_gu.stride(0), C=_lib.ptr(h1), ldc=h1.stride(0), c_batch=0, c_fp32=int(h1.dtype == F32), M=1,
+                                 N=2 * f.expert_ff, K=D, batch=1, epi=_lib.EPI_SILU_GATE, epi_a=0.0, epi_b=0.0)
+            self._check(L.lp_linear_pairs(C.byref(d1), _lib.ptr(idx), f.top, n_pairs, st), "lp_linear_pairs")
+            y = self._empty((n_pairs, D), F32)
+            d2 = _lib.LinearDesc(A=_lib.ptr(h1), lda=h1.stride(0), a_batch=0, a_fp32=int(h1.dtype == F32), W=_lib.ptr(w_dn),
+                                 ldw=w_dn.stride(1), w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=1, N=D,
+                                 K=f.expert_ff, batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
+            self._check(L.lp_linear_pairs(C.byref(d2), _lib.ptr(idx), 1, n_pairs, st), "lp_linear_pairs")
+            return self._moe_combine(f, lw, h, y, self._pair_identity(n_pairs), wts, gate)
         tiles = int(L.lp_moe_max_tiles(n_pairs, f.experts, self.tile_rows))
         tile_group = self._empty((tiles,), I32)
         sorted_token = self._empty((tiles * self.tile_rows,), I32)
@@ -477,13 +492,24 @@ class SeqLMEngine:
                                  ldw=w_dn.stride(1), w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=rows,
                                  N=D, K=f.expert_ff, batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
             self._check(L.lp_linear_grouped(C.byref(d2), _lib.ptr(tile_group), tiles, None, st), "lp_linear_grouped")
+        return self._moe_combine(f, lw, h, y, pair_row, wts, gate)
+
+    def _pair_identity(self, n: int) -> torch.Tensor:
+        t = getattr(self, "_arange", None)
+        if t is None or t.numel() < n:
+            t = self._arange = torch.arange(max(n, 256), dtype=I32, device=self.device)
+        return t
+
+    def _moe_combine(self, f: MoEConfig, lw, h, y, pair_row, wts, gate) -> torch.Tensor:
+        T, D = h.shape
         shared = None
         if f.shared_ff:
             s1 = self.linear(h, lw["ws_gu"], self.act, _lib.EPI_SILU_GATE)
             shared = self.linear(s1, lw["ws_down"], F32)
         out = self._empty((T, D), F32)
-        rc = L.lp_moe_combine(_lib.ptr(y), y.stride(0), _lib.ptr(pair_row), _lib.ptr(wts), f.top, _lib.ptr(shared),
-                              shared.stride(0) if shared is not None else 0, _lib.ptr(gate), _lib.ptr(out), out.stride(0), T, D, st)
+        rc = self.L.lp_moe_combine(_lib.ptr(y), y.stride(0), _lib.ptr(pair_row), _lib.ptr(wts), f.top, _lib.ptr(shared),
+                                   shared.stride(0) if shared is not None else 0, _lib.ptr(gate), _lib.ptr(out), out.stride(0), T, D,
+                                   self._stream())
         self._check(rc, "lp_moe_combine")
         return out
 
