@@ -408,13 +408,14 @@ latent_prep_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int*
 
 // One CTA per (row, head): its warps take every LAT_WARPS-th visible key with an online softmax of their own, then the partial
 // (maximum, denominator, weighted sum) triples are merged.  NR = ceil(kv_rank / 32) accumulators per lane.
-constexpr int LAT_WARPS = 4;
+constexpr int LAT_WARPS = 16;
+constexpr int LAT_SPLIT_MAX_RANK = 512;      // larger latents take the per-row kernel
 constexpr int LAT_MAX_RANK = 1024;
 template <int NR>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, const float* __restrict__ q_abs,
                      long long ldqa, void* __restrict__ out, long long ldo, int out_fp32) {
-  __shared__ float s_acc[LAT_WARPS][LAT_MAX_RANK];
+  __shared__ float s_acc[LAT_WARPS][LAT_SPLIT_MAX_RANK];
   __shared__ float s_mx[LAT_WARPS], s_den[LAT_WARPS];
   const int item = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -433,26 +434,38 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
   }
   const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   float mx = -INFINITY, den = 0.f;
-  for (int j = lo + warp; j <= pos; j += LAT_WARPS) {
-    const float* kv = lat_cache_row(a, seq, j);
-    float cv[NR];
-    float sc = 0.f;
+  // two keys per turn: their score reductions overlap, one rescale of the running sums serves both
+  for (int j = lo + warp; j <= pos; j += 2 * LAT_WARPS) {
+    const bool two = j + LAT_WARPS <= pos;
+    const float* kv0 = lat_cache_row(a, seq, j);
+    const float* kv1 = two ? lat_cache_row(a, seq, j + LAT_WARPS) : kv0;
+    float cv0[NR], cv1[NR];
+    float sc0 = 0.f, sc1 = 0.f;
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
       const int c = lane + 32 * i;
-      cv[i] = c < a.kv_rank ? kv[c] : 0.f;
-      sc = fmaf(qv[i], cv[i], sc);
-      if (c < a.rot_dim) sc = fmaf(qrv[i], kv[a.kv_rank + c], sc);
+      cv0[i] = c < a.kv_rank ? kv0[c] : 0.f;
+      cv1[i] = c < a.kv_rank ? kv1[c] : 0.f;
+      sc0 = fmaf(qv[i], cv0[i], sc0);
+      sc1 = fmaf(qv[i], cv1[i], sc1);
+      if (c < a.rot_dim) {
+        sc0 = fmaf(qrv[i], kv0[a.kv_rank + c], sc0);
+        sc1 = fmaf(qrv[i], kv1[a.kv_rank + c], sc1);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-    sc *= a.scale;
-    const float mn = fmaxf(mx, sc);
-    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the warp's first key
-    const float p = expf(sc - mn);
-    den = den * corr + p;
+    for (int o = 16; o > 0; o >>= 1) {
+      sc0 += __shfl_xor_sync(0xffffffffu, sc0, o);
+      sc1 += __shfl_xor_sync(0xffffffffu, sc1, o);
+    }
+    sc0 *= a.scale;
+    sc1 = two ? sc1 * a.scale : -INFINITY;
+    const float mn = fmaxf(mx, fmaxf(sc0, sc1));
+    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the first turn
+    const float p0 = expf(sc0 - mn), p1 = expf(sc1 - mn);
+    den = den * corr + p0 + p1;
 #pragma unroll
-    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p, cv[i], acc[i] * corr);
+    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p1, cv1[i], fmaf(p0, cv0[i], acc[i] * corr));
     mx = mn;
   }
 #pragma unroll
@@ -485,10 +498,10 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
   }
 }
 
-// Many rows (prompts): one CTA per row, one warp per head (up to LAT_ROW_HEADS heads per CTA), every warp walks all visible keys.
+// Many rows (prompts): one CTA per row and group of LAT_ROW_HEADS heads, one warp per head, every warp walks all visible keys.
 // The heads of a row read the same cache rows at about the same time, so the cache traffic of a row is paid once per CTA (L1), and
 // neighbouring rows overlap in all but one key (L2).
-constexpr int LAT_ROW_HEADS = 16;
+constexpr int LAT_ROW_HEADS = 4;
 template <int NR>
 __global__ void __launch_bounds__(LAT_ROW_HEADS * 32)
 latent_attend_rows_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, const float* __restrict__ q_abs,
@@ -510,26 +523,38 @@ latent_attend_rows_kernel(LatArgs a, int R, const int* __restrict__ row_seq, con
   }
   const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   float mx = -INFINITY, den = 0.f;
-  for (int j = lo; j <= pos; ++j) {
-    const float* kv = lat_cache_row(a, seq, j);
-    float cv[NR];
-    float sc = 0.f;
+  // two keys per turn: their score reductions overlap, one rescale of the running sums serves both
+  for (int j = lo; j <= pos; j += 2 * 1) {
+    const bool two = j + 1 <= pos;
+    const float* kv0 = lat_cache_row(a, seq, j);
+    const float* kv1 = two ? lat_cache_row(a, seq, j + 1) : kv0;
+    float cv0[NR], cv1[NR];
+    float sc0 = 0.f, sc1 = 0.f;
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
       const int c = lane + 32 * i;
-      cv[i] = c < a.kv_rank ? kv[c] : 0.f;
-      sc = fmaf(qv[i], cv[i], sc);
-      if (c < a.rot_dim) sc = fmaf(qrv[i], kv[a.kv_rank + c], sc);
+      cv0[i] = c < a.kv_rank ? kv0[c] : 0.f;
+      cv1[i] = c < a.kv_rank ? kv1[c] : 0.f;
+      sc0 = fmaf(qv[i], cv0[i], sc0);
+      sc1 = fmaf(qv[i], cv1[i], sc1);
+      if (c < a.rot_dim) {
+        sc0 = fmaf(qrv[i], kv0[a.kv_rank + c], sc0);
+        sc1 = fmaf(qrv[i], kv1[a.kv_rank + c], sc1);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-    sc *= a.scale;
-    const float mn = fmaxf(mx, sc);
-    const float corr = expf(mx - mn);
-    const float p = expf(sc - mn);
-    den = den * corr + p;
+    for (int o = 16; o > 0; o >>= 1) {
+      sc0 += __shfl_xor_sync(0xffffffffu, sc0, o);
+      sc1 += __shfl_xor_sync(0xffffffffu, sc1, o);
+    }
+    sc0 *= a.scale;
+    sc1 = two ? sc1 * a.scale : -INFINITY;
+    const float mn = fmaxf(mx, fmaxf(sc0, sc1));
+    const float corr = expf(mx - mn);      // exp(-inf) = 0 on the first turn
+    const float p0 = expf(sc0 - mn), p1 = expf(sc1 - mn);
+    den = den * corr + p0 + p1;
 #pragma unroll
-    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p, cv[i], acc[i] * corr);
+    for (int i = 0; i < NR; ++i) acc[i] = fmaf(p1, cv1[i], fmaf(p0, cv0[i], acc[i] * corr));
     mx = mn;
   }
   const float inv = 1.0f / den;
@@ -665,7 +690,7 @@ extern "C" int lp_latent_attend(const lp_latent_desc* d, int R, const int* row_s
   LP_REQUIRE(d->kv_rank <= LAT_MAX_RANK, "lp_latent_attend: kv_rank=%d > %d is not instantiated", d->kv_rank, LAT_MAX_RANK);
   if (R <= 0) return 0;
   const int nr = (d->kv_rank + 31) / 32;
-  if (R > LP_LATENT_SPLIT_ROWS) {      // prompts: a CTA per row, a warp per head
+  if (R > LP_LATENT_SPLIT_ROWS || d->kv_rank > LAT_SPLIT_MAX_RANK) {      // prompts: a CTA per row, a warp per head
     const dim3 grid(R, (d->heads + LAT_ROW_HEADS - 1) / LAT_ROW_HEADS);
     const int threads = (d->heads < LAT_ROW_HEADS ? d->heads : LAT_ROW_HEADS) * 32;
     if (nr <= 2) latent_attend_rows_kernel<2><<<grid, threads, 0, stream>>>(a, R, row_seq, row_pos, q_abs, ldqa, out, ldo, out_fp32);

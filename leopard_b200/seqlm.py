@@ -27,7 +27,7 @@ from . import _lib
 from .seqcache import SequenceCache
 
 F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
-TENSOR_CORE_MIN_ROWS = 128
+TENSOR_CORE_MIN_ROWS = 64
 MOE_PAIRS_MAX = 64             # up to this many (token, choice) pairs the experts run as one-row weight-streaming problems
 PAGE_TABLE_STEP = 16           # decode batches round their page-table width up to a multiple of this
 

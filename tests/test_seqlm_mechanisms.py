@@ -141,14 +141,14 @@ def test_feed_forward_alone(backend, T, ff):
 
 @pytest.mark.gpu
 def test_large_bf16_products_run_on_the_tensor_cores():
-    """in the serving precision a product of 128 rows or more goes to the tcgen05 GEMM; same result as the fp32-FMA kernels up to
+    """in the serving precision a product of 64 rows or more goes to the tcgen05 GEMM; same result as the fp32-FMA kernels up to
     the rounding of the accumulation order, ragged N and K included, with and without an epilogue"""
     cfg = model([retention_layer()])
     w = O.random_weights(cfg, seed=2)
     eng = make_engine(cfg, w, ("cuda", None), "bfloat16")
-    assert eng.tensor_core_rows == 128
+    assert eng.tensor_core_rows == 64
     g = torch.Generator().manual_seed(5)
-    for M, N, K in ((130, 128, 64), (333, 328, 136), (1000, 784, 320)):
+    for M, N, K in ((64, 128, 64), (130, 128, 64), (333, 328, 136), (1000, 784, 320)):
         a = torch.randn(M, K, generator=g).to(BF16).cuda()
         wt = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(BF16).cuda()
         want = a.double() @ wt.double().T
@@ -159,4 +159,4 @@ def test_large_bf16_products_run_on_the_tensor_cores():
         assert rel_err(eng.linear(a, wt, F32, _lib.EPI_SILU_GATE), gate * torch.sigmoid(gate) * up) < 1e-5
         eng.tensor_core_rows = None                 # the same call on the fp32-FMA kernel
         assert rel_err(eng.linear(a, wt, F32), want) < 1e-5
-        eng.tensor_core_rows = 128
+        eng.tensor_core_rows = 64
