@@ -272,17 +272,20 @@ def run(args):
     prompt = 4096
     L = _lib.stream32_lib()
     n0 = L.lp_launch_count()
+    only = [x for x in (getattr(args, "seqlm_sizes", None) or "").split(",") if x]
     for name, s in SIZES.items():
+        if only and name not in only:
+            continue
         sizes.append(bench_size(name, s, dev, args.steps, max(args.warmup, 3), peaks, prompt))
         try:
             twins.append(bench_llama_twin(name, s, dev, args.steps, max(args.warmup, 3), prompt))
         except Exception as e:      # a width the Llama-style path does not take: say so, keep the rest
             twins.append({"size": name, "unavailable": f"{type(e).__name__}: {e}"[:300]})
-    mid = sizes[1]
+    mid = sizes[min(1, len(sizes) - 1)]
     line = {"metric": "seqlm_prefill_tokens_per_s", "value": mid["prefill_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": mid["prefill_ms"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
-            "config": {"model": "Zudalorn 4-layer stack, width 2048", "global_batch": 1, "seq_len": prompt, "parallelism": "single GPU",
+            "config": {"model": f"Zudalorn 4-layer stack, {mid['size']}", "global_batch": 1, "seq_len": prompt, "parallelism": "single GPU",
                        "cache_policy": "weights + activations of a step exceed L2 at every size"},
             "gpu_launches": int(L.lp_launch_count() - n0), "peaks": peaks, "fp32_fma_peak_tflops": round(FP32_FMA_TFLOPS, 1),
             "sizes": sizes, "llama_style_twin": twins}

@@ -134,21 +134,25 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_tile_kernel(LinArgs a) {
 }
 
 // Few rows (M <= 8): one warp per output column, the lanes split K; the weight row is read once with 16-byte loads when K allows.
-constexpr int ROWS_MAX = 8, ROWS_WARPS = 8;
+// The rows of A are staged in shared memory K-chunk by K-chunk (fp32, laid out so that the lanes' eight consecutive k of one
+// 16-byte weight load fall into different banks) and shared by the CTA's eight columns.
+constexpr int ROWS_MAX = 8, ROWS_WARPS = 8, ROWS_KC = 512, ROWS_LD = ROWS_KC / 8 + 1;
+__device__ __forceinline__ int rows_slot(int kk) { return (kk & 7) * ROWS_LD + (kk >> 3); }
 template <typename AT, typename CT, bool GATED>
 __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a) {
+  __shared__ float As[ROWS_MAX][8 * ROWS_LD];
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * ROWS_WARPS + (threadIdx.x >> 5);
   const int z = blockIdx.z;
   const int n_out = GATED ? a.N / 2 : a.N;
-  if (n >= n_out) return;
+  const bool active = n < n_out;
   const bool pairs = a.z_group != nullptr;
   const int M = pairs ? 1 : a.M;
   const AT* A = reinterpret_cast<const AT*>(a.A) + (pairs ? (long long)(z / a.a_div) * a.lda : (long long)z * a.a_batch);
   const bf16* W = a.W + (long long)(pairs ? a.z_group[z] : z) * a.w_batch;
   CT* C = reinterpret_cast<CT*>(a.C) + (pairs ? (long long)z * a.ldc : (long long)z * a.c_batch);
-  const bf16* w1 = W + (long long)n * a.ldw;
-  const bf16* w2 = W + (long long)(n + n_out) * a.ldw;
+  const bf16* w1 = W + (long long)(active ? n : 0) * a.ldw;
+  const bf16* w2 = W + (long long)(active ? n + n_out : 0) * a.ldw;
   float acc[ROWS_MAX], acc2[GATED ? ROWS_MAX : 1];
 #pragma unroll
   for (int m = 0; m < ROWS_MAX; ++m) {
@@ -156,41 +160,52 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
     if (GATED) acc2[m] = 0.f;
   }
   const bool vec = (a.K % 8 == 0) && (a.ldw % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
-  if (vec) {
-    for (int k = lane * 8; k < a.K; k += 256) {
-      const uint4 u1 = *reinterpret_cast<const uint4*>(w1 + k);
-      uint4 u2 = u1;
-      if (GATED) u2 = *reinterpret_cast<const uint4*>(w2 + k);
-      float f1[8], f2[8];
-      bf16x8_to_f32(u1, f1);
-      bf16x8_to_f32(u2, f2);
+  for (int k0 = 0; k0 < a.K; k0 += ROWS_KC) {
+    const int kc = min(ROWS_KC, a.K - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < M * kc; i += blockDim.x) {
+      const int m = i / kc, kk = i % kc;
+      As[m][rows_slot(kk)] = lin_load(A + (long long)m * a.lda + k0 + kk);
+    }
+    __syncthreads();
+    if (!active) continue;
+    if (vec) {
+      for (int kk = lane * 8; kk < kc; kk += 256) {
+        const uint4 u1 = *reinterpret_cast<const uint4*>(w1 + k0 + kk);
+        uint4 u2 = u1;
+        if (GATED) u2 = *reinterpret_cast<const uint4*>(w2 + k0 + kk);
+        float f1[8], f2[8];
+        bf16x8_to_f32(u1, f1);
+        bf16x8_to_f32(u2, f2);
+        const int base = kk >> 3;
 #pragma unroll
-      for (int m = 0; m < ROWS_MAX; ++m) {
-        if (m < M) {
-          const AT* ar = A + (long long)m * a.lda + k;
+        for (int m = 0; m < ROWS_MAX; ++m) {
+          if (m < M) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float x = lin_load(ar + i);
-            acc[m] = fmaf(x, f1[i], acc[m]);
-            if (GATED) acc2[m] = fmaf(x, f2[i], acc2[m]);
+            for (int i = 0; i < 8; ++i) {
+              const float x = As[m][i * ROWS_LD + base];
+              acc[m] = fmaf(x, f1[i], acc[m]);
+              if (GATED) acc2[m] = fmaf(x, f2[i], acc2[m]);
+            }
+          }
+        }
+      }
+    } else {
+      for (int kk = lane; kk < kc; kk += 32) {
+        const float f1 = __bfloat162float(w1[k0 + kk]);
+        const float f2 = GATED ? __bfloat162float(w2[k0 + kk]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < ROWS_MAX; ++m) {
+          if (m < M) {
+            const float x = As[m][rows_slot(kk)];
+            acc[m] = fmaf(x, f1, acc[m]);
+            if (GATED) acc2[m] = fmaf(x, f2, acc2[m]);
           }
         }
       }
     }
-  } else {
-    for (int k = lane; k < a.K; k += 32) {
-      const float f1 = __bfloat162float(w1[k]);
-      const float f2 = GATED ? __bfloat162float(w2[k]) : 0.f;
-#pragma unroll
-      for (int m = 0; m < ROWS_MAX; ++m) {
-        if (m < M) {
-          const float x = lin_load(A + (long long)m * a.lda + k);
-          acc[m] = fmaf(x, f1, acc[m]);
-          if (GATED) acc2[m] = fmaf(x, f2, acc2[m]);
-        }
-      }
-    }
   }
+  if (!active) return;
 #pragma unroll
   for (int m = 0; m < ROWS_MAX; ++m) {
     if (m < M) {

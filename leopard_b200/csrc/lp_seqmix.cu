@@ -27,6 +27,7 @@ namespace lp {
 typedef __nv_bfloat16 bf16;
 
 constexpr int RET_CHUNK = LP_RETENTION_CHUNK;
+constexpr int RET_CHUNK_THREADS = 256;      // CTA size of the two chunk kernels (their loops stride by blockDim)
 
 // element d of one head's vector x at position pos: rotated when d < rot_dims, copied otherwise
 __device__ __forceinline__ float rot_elem(const float* __restrict__ x, int d, int rot_dims, int layout, const float* __restrict__ inv_freq,
@@ -65,7 +66,7 @@ struct RetArgs {
 
 // (1) U[chunk][head] = sum_j decay^(len-1-j) k_j v_j^T.  4 x 4 outputs per thread; a thread's four columns are vdim/4 apart, so that
 // the threads of a warp read consecutive shared-memory words.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(RET_CHUNK_THREADS)
 retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
                              const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, float* __restrict__ ws) {
   extern __shared__ float dyn_smem[];
@@ -157,7 +158,7 @@ retention_scan_kernel(RetArgs a, const int* __restrict__ seq_chunk0, const int* 
 
 // (3) o_i = decay^(i+1) q_i^T S_start + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j; then o / rms(o) * silu(g).  The chunk's start state is
 // staged in shared memory (stage_s; read from global when a head is too large for that); 4 x 4 outputs per thread.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(RET_CHUNK_THREADS)
 retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
                            const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const float* __restrict__ ws, int stage_s) {
   extern __shared__ float dyn_smem[];
@@ -640,12 +641,12 @@ extern "C" int lp_retention_prefill(const lp_retention_desc* d, int n_seqs, int 
   if (stage_s) smem3 += (size_t)d->dim * vdimp * sizeof(float);
   LP_CHECK_CUDA(ensure_smem(retention_chunk_state_kernel, smem1, g_smem_chunk_state));
   LP_CHECK_CUDA(ensure_smem(retention_chunk_out_kernel, smem3, g_smem_chunk_out));
-  retention_chunk_state_kernel<<<dim3(n_chunks, d->heads), 128, smem1, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
+  retention_chunk_state_kernel<<<dim3(n_chunks, d->heads), RET_CHUNK_THREADS, smem1, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w);
   LP_CHECK_CUDA(cudaGetLastError());
   retention_scan_kernel<<<dim3(n_seqs, d->heads, (d->dim * d->vdim + SCAN_THREADS - 1) / SCAN_THREADS), SCAN_THREADS, 0, stream>>>(
       a, seq_chunk0, chunk_len, seq_pos0, seq_slot, w);
   LP_CHECK_CUDA(cudaGetLastError());
-  retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), 128, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w,
+  retention_chunk_out_kernel<<<dim3(n_chunks, d->heads), RET_CHUNK_THREADS, smem3, stream>>>(a, chunk_seq, chunk_row0, chunk_len, seq_row0, seq_pos0, w,
                                                                                 stage_s);
   LP_CHECK_CUDA(cudaGetLastError());
   note_launch(3);

@@ -32,7 +32,7 @@ def build_emulated(out: Path) -> Path:
         '#include "host_emu.h"\nextern "C" {\nconst char* lp_last_error(void) { return lp::g_emu_err; }\n'
         'long long lp_launch_count(void) { return 0; }\nint lp_abi_version(void) { return 3; }\n}\n')
     lib = out / "libstream32_emu.so"
-    r = subprocess.run(["g++", "-std=c++20", "-O2", "-pthread", "-shared", "-fPIC", "-ffp-contract=off", "-I", str(out),
+    r = subprocess.run(["g++", "-std=c++20", "-O2", "-pthread", "-shared", "-fPIC", "-ffp-contract=off", "-fno-strict-aliasing", "-I", str(out),
                         "-I", str(ROOT / "tests/emu"), "-I", str(ROOT / "include"), *units, str(out / "common_emu.cpp"), "-o", str(lib)],
                        capture_output=True, text=True)
     if r.returncode != 0:
