@@ -687,10 +687,10 @@ extern "C" int lp_latent_attend(const lp_latent_desc* d, int R, const int* row_s
   LatArgs a;
   if (int rc = fill_lat(a, d)) return rc;
   LP_REQUIRE(q_abs != nullptr && out != nullptr && row_seq != nullptr && row_pos != nullptr, "lp_latent_attend: null operand");
-  LP_REQUIRE(d->rot_dim <= d->kv_rank || d->rot_dim <= 32, "lp_latent_attend: rot_dim=%d must not exceed kv_rank=%d", d->rot_dim, d->kv_rank);
-  LP_REQUIRE(d->kv_rank <= LAT_MAX_RANK, "lp_latent_attend: kv_rank=%d > %d is not instantiated", d->kv_rank, LAT_MAX_RANK);
+  LP_REQUIRE(d->kv_rank <= LAT_MAX_RANK && d->rot_dim <= LAT_MAX_RANK, "lp_latent_attend: kv_rank=%d / rot_dim=%d > %d is not instantiated",
+             d->kv_rank, d->rot_dim, LAT_MAX_RANK);
   if (R <= 0) return 0;
-  const int nr = (d->kv_rank + 31) / 32;
+  const int nr = ((d->kv_rank > d->rot_dim ? d->kv_rank : d->rot_dim) + 31) / 32;      // lanes hold both vectors strided by 32
   if (R > LP_LATENT_SPLIT_ROWS || d->kv_rank > LAT_SPLIT_MAX_RANK) {      // prompts: a CTA per row, a warp per head
     const dim3 grid(R, (d->heads + LAT_ROW_HEADS - 1) / LAT_ROW_HEADS);
     const int threads = (d->heads < LAT_ROW_HEADS ? d->heads : LAT_ROW_HEADS) * 32;

@@ -88,8 +88,8 @@ def test_rotary_table_with_rescaling():
 
 @pytest.mark.parametrize("layer", [retention_layer(), retention_layer(heads=1, dim=6, vdim=40, rot_dims=6, decay=(0.999,)),
                                    latent_layer(), latent_layer(heads=3, dim=2, rot_dim=6, vdim=3, kv_rank=40, window=3, scaling=False),
-                                   latent_layer(window=None)],
-                         ids=["retention", "retention-wide-v", "latent", "latent-rank40-w3", "latent-no-window"])
+                                   latent_layer(window=None), latent_layer(heads=2, dim=2, rot_dim=36, vdim=3, kv_rank=8, window=4)],
+                         ids=["retention", "retention-wide-v", "latent", "latent-rank40-w3", "latent-no-window", "latent-rot-wider-than-rank"])
 def test_mixer_alone_prefill_and_decode(backend, layer):
     """one mixer between its norms, no feed-forward: a whole prompt (several retention chunks / windows), then token by token"""
     cfg, w, eng = _engine_1layer(layer, backend)
