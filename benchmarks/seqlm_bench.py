@@ -8,12 +8,11 @@ Per size: a 4-layer stack [retention + dense, retention + MoE, windowed latent a
   kernels   device time per native entry point of one prefill step and one decode step (CUDA events around every call) with the
             rate each reaches: TFLOP/s of the measured cuBLAS bf16 peak for the tcgen05 GEMM, of the fp32 FMA peak for the 32-bit
             mixers, GB/s of the measured copy bandwidth for the weight-streaming decode kernels.
-One JSON line in the bench contract's shape; `value` is the prefill throughput of the middle size.
+One JSON line in the shape bench.py prints for its other workloads; `value` is the prefill throughput of the middle size.
 """
 from __future__ import annotations
 
 import json
-import math
 import time
 from collections import defaultdict
 
@@ -29,7 +28,7 @@ FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12     # SMs x FMA lanes x 2 x max
 
 
 def zudalorn_config(s):
-    ret = {"heads": s["heads"], "dim": HEAD, "vdim": HEAD, "decay": [1 - 2.0 ** (-5 - 5 * i / max(s["heads"] - 1, 1)) for i in range(s["heads"])],
+    ret = {"heads": s["heads"], "dim": HEAD, "vdim": HEAD, "decay": [1 - 2.0 ** (-4 - 4 * i / max(s["heads"] - 1, 1)) for i in range(s["heads"])],
            "rot": {"base": 1e6, "dims": HEAD}}
     lat = {"heads": s["heads"], "dim": HEAD, "rot_dim": 64, "vdim": HEAD, "kv_rank": s["kv_rank"], "scale": (HEAD + 64) ** -0.5,
            "mask": {"size": s["window"]},

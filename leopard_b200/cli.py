@@ -42,7 +42,6 @@ def cmd_generate(args) -> int:
 
 
 def cmd_trace(args) -> int:
-    import numpy as np
     from .seqlm import StepEntry
     eng = _load(args)
     if not hasattr(eng, "step"):

@@ -4,7 +4,6 @@ taken again, keys at the edges of a sliding window and of cache pages, a far tok
 happen to be one, both precisions, and greedy generation through the scheduler and the command line.  On the kernel sources under
 the CPU emulator and, marked gpu, on the native library."""
 import json
-import math
 
 import pytest
 import torch
@@ -13,7 +12,7 @@ from leopard_b200 import zudalorn
 from leopard_b200.scheduler import Request, Scheduler, generate
 from leopard_b200.seqlm import StepEntry
 from oracle import seqlm as O
-from seqlm_common import (TOL, backend, dense, emu_lib, latent_layer, make_engine, mixed_model, model, moe, plain_model,  # noqa: F401
+from seqlm_common import (TOL, backend, emu_lib, latent_layer, make_engine, mixed_model, model, plain_model,  # noqa: F401  (fixtures)
                           rel_err, retention_layer)
 
 

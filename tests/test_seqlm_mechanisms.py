@@ -2,7 +2,6 @@
 layer (both kernels, every epilogue, per-head batches, ragged shapes), scalar-gain RMS norm with the residual update, rotary tables
 with frequency rescaling, retention, windowed latent attention, the grouped-choice router, the expert feed-forward and xIELU.  Every
 test runs on the kernel SOURCES under the CPU emulator (tests/emu) and, marked gpu, on the native library."""
-import ctypes as C
 import math
 
 import pytest
