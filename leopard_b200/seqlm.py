@@ -29,6 +29,7 @@ from .seqcache import SequenceCache
 F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
 TENSOR_CORE_MIN_ROWS = 64
 MOE_PAIRS_MAX = 64             # up to this many (token, choice) pairs the experts run as one-row weight-streaming problems
+MAX_DECODE_GRAPHS = 32         # captured decode layouts kept at a time
 PAGE_TABLE_STEP = 16           # decode batches round their page-table width up to a multiple of this
 
 
@@ -542,6 +543,9 @@ class SeqLMEngine:
                 return self._forward(b, b.want_rows if b.n_want else None)
             for old in [k for k in self._graphs if k[1] != self.cache.generation]:
                 del self._graphs[old]                      # pools were reallocated: those graphs point at freed memory
+            if len(self._graphs) >= MAX_DECODE_GRAPHS:      # a bound on what the captured layouts may hold
+                self._graphs.clear()
+                self._seen.clear()
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()
             with torch.cuda.graph(graph):
