@@ -582,20 +582,22 @@ int lp_parity_softmax(float* scores, long long ld, int Tq, int Tk, float scale, 
  * mechanisms are separate entry points with their constants as arguments, so that a model description (a list of layers) composes
  * them: csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_moe.cu.
  * ------------------------------------------------------------------------------------------------------------------ */
-enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2 };
+enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2, LP_EPI_RELU2 = 3 };
 enum lp_rot_layout { LP_ROT_HALF = 0, LP_ROT_INTERLEAVED = 1 };
 #define LP_RETENTION_CHUNK 32
 #define LP_LATENT_SPLIT_ROWS 16   /* lp_latent_attend: up to this many rows a CTA per (row, head) splits the keys over its warps */
 
 /* C[M, N'] = epi(A[M, K] W[N, K]^T), `batch` problems `*_batch` elements apart.  A: fp32 (a_fp32) or bf16; W: bf16; C: fp32 (c_fp32) or
  * bf16.  epi XIELU: a z^2 + z/2 (z > 0), b (exp(z) - 1 - z) + z/2 (z <= 0) with a = epi_a, b = epi_b.  epi SILU_GATE: W = [gate rows;
- * up rows], N' = N / 2, C = silu(gate) * up.  fp32 FMA accumulation in K order. */
+ * up rows], N' = N / 2, C = silu(gate) * up.  epi RELU2: max(z, 0)^2.  fp32 FMA accumulation in K order.  c_accum != 0: the result
+ * is not stored but added, C <- C + c_scale * epi(...) (x <- x + m * sublayer(x) in the product's own store). */
 typedef struct lp_linear_desc {
   const void* A; long long lda; long long a_batch; int a_fp32;
   const void* W; long long ldw; long long w_batch;
   void* C; long long ldc; long long c_batch; int c_fp32;
   int M, N, K, batch;
   int epi; float epi_a, epi_b;
+  int c_accum; float c_scale;
 } lp_linear_desc;
 int lp_linear(const lp_linear_desc* desc, void* stream);
 /* row tiles of lp_linear_tile_rows() rows, each multiplied by the weight of group tile_group[tile] (w_batch elements apart; < 0: the
@@ -605,7 +607,9 @@ int lp_linear_tile_rows(void);
 /* n_pairs one-row problems: problem z = A row z / a_div times the weight of group pair_group[z] -> C row z (weight-streaming kernel) */
 int lp_linear_pairs(const lp_linear_desc* desc, const int* pair_group, int a_div, int n_pairs, void* stream);
 
-int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float* out, long long ldo, int D, void* stream);
+/* out[r, :] = table[ids[r], :] * scale */
+int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float scale, float* out, long long ldo, int D,
+                      void* stream);
 /* y = x / sqrt(mean(x^2) + eps) * gain_scalar (* gain_vec[c]); written to `out` (fp32 or bf16) or added to `accum` (fp32) */
 int lp_rmsnorm_f32(const float* x, long long ldx, int M, int D, float gain_scalar, const float* gain_vec, float eps, void* out,
                    long long ldo, int out_fp32, float* accum, long long ld_accum, void* stream);
@@ -650,6 +654,61 @@ int lp_latent_prep(const lp_latent_desc* desc, int R, const int* row_seq, const 
 /* q_abs fp32 [rows, heads * kv_rank] = per-head W_uk^T q_unrotated; out [rows, heads * kv_rank] = softmax-weighted sum of cached c */
 int lp_latent_attend(const lp_latent_desc* desc, int R, const int* row_seq, const int* row_pos, const float* q_abs, long long ldqa,
                      void* out, long long ldo, int out_fp32, void* stream);
+
+/* Grouped-query attention over a paged cache of rows [keys (kv_heads x dim) | values (kv_heads x vdim)] fp32, with the visibility
+ * rules and score options of sliding-window designs as parameters (csrc/lp_winattn.cu).  Query at position i of a request sees
+ *   - tokens j with 0 <= i - j < window (window <= 0: every j <= i),
+ *   - the first keep_first tokens of the request, whatever their distance (they keep their own positions),
+ *   - with pool = P > 0: one key / value per block of P tokens that lies wholly before the window (block b = positions bP .. bP+P-1
+ *     is seen when bP + P - 1 <= i - window); they are the means of the block's cached key and value rows, kept in a second paged
+ *     pool `pooled` with one row per block (pooled_table: pages of block rows per request).
+ * score = q . k * scale, then softcap * tanh(score / softcap) when softcap > 0.  One softmax over everything visible; sink != 0 adds
+ * 1 to its denominator (a key of score 0 without a value).  Query head h reads key / value head h / (heads / kv_heads).
+ * norm_mode: RMS norm of q and k before rotation — LP_QKNORM_NONE, LP_QKNORM_HEAD (over each head's dim, gains [dim] shared by the
+ * heads) or LP_QKNORM_FULL (over the whole projection, gains [heads * dim] and [kv_heads * dim]).  q and k are rotated on the first
+ * rot_dims dimensions of a head; with v_inv_freq the values are rotated over v_rot_dims (cached so) and every head's output is
+ * turned back by its query's position. */
+enum lp_qknorm_mode { LP_QKNORM_NONE = 0, LP_QKNORM_HEAD = 1, LP_QKNORM_FULL = 2 };
+typedef struct lp_window_attn_desc {
+  float* qkv; long long ld; int q_off, k_off, v_off;     /* fp32 rows of the fused projection; q is normalised and rotated in place */
+  int heads, kv_heads, dim, vdim;
+  int norm_mode; const float* q_gain; const float* k_gain; float eps;
+  const float* inv_freq; int rot_dims; int rot_layout; float rot_mscale;
+  const float* v_inv_freq; int v_rot_dims; int v_rot_layout;
+  float* cache; int page_size; const int* page_table; int max_pages;
+  float* pooled; const int* pooled_table; int max_pooled_pages; int pool;
+  int window; int keep_first;
+  float scale, softcap; int sink;
+} lp_window_attn_desc;
+/* norm + rotation of the step's rows; keys and values go to the request's pages */
+int lp_window_attn_prep(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* stream);
+/* the block means of every block that the step completed: request s brought seq_len = seq_row0[s+1] - seq_row0[s] tokens from position
+ * seq_pos0[s]; max_new_blocks bounds the blocks one request completes in this step (1 for one-token steps) */
+int lp_window_attn_pool(const lp_window_attn_desc* desc, int n_seqs, const int* seq_row0, const int* seq_pos0, int max_new_blocks,
+                        void* stream);
+/* out [rows, heads * vdim] fp32 or bf16 */
+int lp_window_attn(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
+                   int out_fp32, void* stream);
+
+/* minGRU: z = sigmoid(zxg[:, z_off + c] + z_bias[c]), u = zxg[:, x_off + c] + x_bias[c], candidate = u + 1/2 (u >= 0) or sigmoid(u)
+ * (u < 0); S_t = (1 - z) S_(t-1) + z candidate per channel, out = S_t * silu(zxg[:, g_off + c]).  state fp32 [slots][width], carried
+ * between steps; a request at position 0 starts from zero without reading its slot.  Prompts run as a chunked scan over the chunk
+ * tables of lp_retention_prefill (workspace: 2 * n_chunks * width floats). */
+typedef struct lp_mingru_desc {
+  const float* zxg; long long ld; int z_off, x_off, g_off;
+  int width;
+  const float* z_bias; const float* x_bias;
+  float* state; long long slot_stride;
+  void* out; long long ldo; int out_fp32;
+} lp_mingru_desc;
+size_t lp_mingru_workspace_bytes(int n_chunks, int width);
+int lp_mingru_prefill(const lp_mingru_desc* desc, int n_seqs, int n_chunks, const int* seq_row0, const int* seq_pos0, const int* seq_slot,
+                      const int* seq_chunk0, const int* chunk_seq, const int* chunk_row0, const int* chunk_len, void* workspace,
+                      size_t workspace_bytes, void* stream);
+int lp_mingru_decode(const lp_mingru_desc* desc, int n_seqs, const int* seq_row0, const int* seq_pos0, const int* seq_slot, void* stream);
+
+/* y <- y + alpha * x over fp32 [M, N] (the residual update after a product that ran on the tensor cores) */
+int lp_axpy_f32(float* y, long long ldy, const float* x, long long ldx, float alpha, int M, int N, void* stream);
 
 int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
                  const float* correction, int n_groups, int keep_groups, int top, const void* w_gate, int* idx_out, float* w_out,

@@ -77,7 +77,8 @@ class ProfileRecord(C.Structure):
 
 _P = C.POINTER
 
-EPI_NONE, EPI_XIELU, EPI_SILU_GATE = 0, 1, 2
+EPI_NONE, EPI_XIELU, EPI_SILU_GATE, EPI_RELU2 = 0, 1, 2, 3
+QKNORM_NONE, QKNORM_HEAD, QKNORM_FULL = 0, 1, 2
 ROT_HALF, ROT_INTERLEAVED = 0, 1
 RETENTION_CHUNK = 32
 
@@ -86,7 +87,22 @@ class LinearDesc(C.Structure):
     """lp_linear_desc (include/leopard_b200.h)."""
     _fields_ = [("A", _vp), ("lda", _ll), ("a_batch", _ll), ("a_fp32", _i), ("W", _vp), ("ldw", _ll), ("w_batch", _ll), ("C", _vp),
                 ("ldc", _ll), ("c_batch", _ll), ("c_fp32", _i), ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("epi", _i),
-                ("epi_a", _f), ("epi_b", _f)]
+                ("epi_a", _f), ("epi_b", _f), ("c_accum", _i), ("c_scale", _f)]
+
+
+class WindowAttnDesc(C.Structure):
+    """lp_window_attn_desc (include/leopard_b200.h)."""
+    _fields_ = [("qkv", _vp), ("ld", _ll), ("q_off", _i), ("k_off", _i), ("v_off", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i),
+                ("vdim", _i), ("norm_mode", _i), ("q_gain", _vp), ("k_gain", _vp), ("eps", _f), ("inv_freq", _vp), ("rot_dims", _i),
+                ("rot_layout", _i), ("rot_mscale", _f), ("v_inv_freq", _vp), ("v_rot_dims", _i), ("v_rot_layout", _i), ("cache", _vp),
+                ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("pooled", _vp), ("pooled_table", _vp),
+                ("max_pooled_pages", _i), ("pool", _i), ("window", _i), ("keep_first", _i), ("scale", _f), ("softcap", _f), ("sink", _i)]
+
+
+class MinGRUDesc(C.Structure):
+    """lp_mingru_desc (include/leopard_b200.h)."""
+    _fields_ = [("zxg", _vp), ("ld", _ll), ("z_off", _i), ("x_off", _i), ("g_off", _i), ("width", _i), ("z_bias", _vp), ("x_bias", _vp),
+                ("state", _vp), ("slot_stride", _ll), ("out", _vp), ("ldo", _ll), ("out_fp32", _i)]
 
 
 class RetentionDesc(C.Structure):
@@ -192,7 +208,14 @@ _SIGS = {
     "lp_linear_grouped": (_i, [C.POINTER(LinearDesc), _vp, _i, _vp, _vp]),
     "lp_linear_tile_rows": (_i, []),
     "lp_linear_pairs": (_i, [C.POINTER(LinearDesc), _vp, _i, _i, _vp]),
-    "lp_embed_rows_f32": (_i, [_vp, _i, _vp, _ll, _i, _vp, _ll, _i, _vp]),
+    "lp_embed_rows_f32": (_i, [_vp, _i, _vp, _ll, _i, _f, _vp, _ll, _i, _vp]),
+    "lp_axpy_f32": (_i, [_vp, _ll, _vp, _ll, _f, _i, _i, _vp]),
+    "lp_window_attn_prep": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp]),
+    "lp_window_attn_pool": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp]),
+    "lp_window_attn": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_mingru_workspace_bytes": (_sz, [_i, _i]),
+    "lp_mingru_prefill": (_i, [C.POINTER(MinGRUDesc), _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "lp_mingru_decode": (_i, [C.POINTER(MinGRUDesc), _i, _vp, _vp, _vp, _vp]),
     "lp_rmsnorm_f32": (_i, [_vp, _ll, _i, _i, _f, _vp, _f, _vp, _ll, _i, _vp, _ll, _vp]),
     "lp_glu_f32": (_i, [_vp, _ll, _i, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp]),
     "lp_retention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
@@ -241,14 +264,15 @@ def lib():
     return _lib
 
 
-# ---- the 32-bit residual-stream entry points (csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_moe.cu) -----------------------------------
+# ---- the 32-bit residual-stream entry points (csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_winattn.cu, lp_mingru.cu, lp_moe.cu) -----------------------------------
 # They need none of the tcgen05 translation units, so a model that uses only them can run from a library of its own that compiles in
 # seconds (build.build_native("stream32")); the full library contains the same symbols and is preferred when it is already built.
 STREAM32_LIB_PATH = PKG / "lib" / "libleopard_stream32.so"
 STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_linear", "lp_linear_grouped", "lp_linear_tile_rows", "lp_linear_pairs",
                     "lp_embed_rows_f32", "lp_rmsnorm_f32", "lp_glu_f32", "lp_retention_workspace_bytes", "lp_retention_prefill",
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
-                    "lp_moe_combine")
+                    "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_mingru_workspace_bytes",
+                    "lp_mingru_prefill", "lp_mingru_decode")
 STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None
 

@@ -2,7 +2,8 @@
 //
 //   lp_linear          C[M,N] = epi(A[M,K] · W[N,K]^T): A fp32 or bf16, W bf16 (nn.Linear layout), C fp32 or bf16, accumulation in
 //                      fp32 FMAs in index order of K (no tensor-core rounding: with fp32 A this is a true 32-bit product, the bf16
-//                      weight is exact in fp32).  Epilogues: none, xIELU, gated SiLU (W = [gate rows; up rows], C has N/2 columns).
+//                      weight is exact in fp32).  Epilogues: none, xIELU, squared relu, gated SiLU (W = [gate rows; up rows], C has
+//                      N/2 columns).  With c_accum the result is scaled and ADDED to C (the residual update of a pre-norm layer).
 //                      `batch` independent problems with element strides (per-head products of latent attention).
 //                      Two kernels: a 64 x 64 x 16 shared-memory tile kernel (prefill), and a weight-streaming kernel with one warp
 //                      per output column for M <= 8 rows (decode: every weight byte is read once, 16-byte loads).
@@ -27,6 +28,7 @@ struct LinArgs {
   void* C; long long ldc; long long c_batch;
   int M, N, K;            // N = rows of W that are used (gated: 2 x output columns)
   int epi; float e0, e1;  // lp_linear_epi and its two constants
+  int c_accum; float c_scale;   // C <- C + c_scale * epi(A W^T) instead of C <- epi(A W^T)
   const int* a_rows;      // grouped: source row of each sorted row, or NULL
   const int* tile_group;  // grouped: group of each row tile, or NULL
   const int* z_group;     // pairs (rows kernel): weight group of problem z, or NULL; problem z reads A row z / a_div and writes C row z
@@ -53,6 +55,10 @@ __device__ __forceinline__ float xielu_f(float z, float a, float b) {
 __device__ __forceinline__ float silu32_f(float z) { return z / (1.0f + expf(-z)); }
 
 __device__ __forceinline__ float lin_epi(int epi, float v, float e0, float e1) {
+  if (epi == LP_EPI_RELU2) {      // the square of relu
+    const float r = fmaxf(v, 0.f);
+    return r * r;
+  }
   return epi == LP_EPI_XIELU ? xielu_f(v, e0, e1) : v;
 }
 
@@ -128,6 +134,7 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_tile_kernel(LinArgs a) {
       const int n = n0 + tn + j;
       if (n >= n_out) continue;
       float v = GATED ? silu32_f(acc[i][j]) * acc2[i][j] : lin_epi(a.epi, acc[i][j], a.e0, a.e1);
+      if (a.c_accum) v = fmaf(a.c_scale, v, lin_load(C + (long long)m * a.ldc + n));
       lin_store(C + (long long)m * a.ldc + n, v);
     }
   }
@@ -216,7 +223,8 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
         if (GATED) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
       }
       if (lane == 0) {
-        const float v = GATED ? silu32_f(s) * s2 : lin_epi(a.epi, s, a.e0, a.e1);
+        float v = GATED ? silu32_f(s) * s2 : lin_epi(a.epi, s, a.e0, a.e1);
+        if (a.c_accum) v = fmaf(a.c_scale, v, lin_load(C + (long long)m * a.ldc + n));
         lin_store(C + (long long)m * a.ldc + n, v);
       }
     }
@@ -261,7 +269,7 @@ extern "C" int lp_linear(const lp_linear_desc* d, void* stream_) {
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr, "lp_linear: null operand");
   LP_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0 && d->batch >= 1, "lp_linear: bad problem M=%d N=%d K=%d batch=%d", d->M, d->N, d->K,
              d->batch);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_SILU_GATE, "lp_linear: bad epilogue %d", d->epi);
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear: bad epilogue %d", d->epi);
   LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear: the gated epilogue needs an even N (gate rows, then up rows)");
   if (d->M == 0) return 0;
   LinArgs a;
@@ -269,7 +277,7 @@ extern "C" int lp_linear(const lp_linear_desc* d, void* stream_) {
   a.W = reinterpret_cast<const bf16*>(d->W); a.ldw = d->ldw; a.w_batch = d->w_batch;
   a.C = d->C; a.ldc = d->ldc; a.c_batch = d->c_batch;
   a.M = d->M; a.N = d->N; a.K = d->K;
-  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
+  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = nullptr; a.a_div = 1;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, d->batch, (d->M + LIN_BM - 1) / LIN_BM, true, stream);
 }
@@ -281,7 +289,7 @@ extern "C" int lp_linear_pairs(const lp_linear_desc* d, const int* pair_group, i
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr && pair_group != nullptr, "lp_linear_pairs: null operand");
   LP_REQUIRE(d->N > 0 && d->K > 0 && a_div >= 1 && n_pairs >= 0 && n_pairs <= 65535, "lp_linear_pairs: bad problem N=%d K=%d pairs=%d", d->N,
              d->K, n_pairs);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_SILU_GATE, "lp_linear_pairs: bad epilogue %d", d->epi);
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear_pairs: bad epilogue %d", d->epi);
   LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear_pairs: the gated epilogue needs an even N");
   if (n_pairs == 0) return 0;
   LinArgs a;
@@ -289,7 +297,7 @@ extern "C" int lp_linear_pairs(const lp_linear_desc* d, const int* pair_group, i
   a.W = reinterpret_cast<const bf16*>(d->W); a.ldw = d->ldw; a.w_batch = d->w_batch;
   a.C = d->C; a.ldc = d->ldc; a.c_batch = 0;
   a.M = 1; a.N = d->N; a.K = d->K;
-  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
+  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = pair_group; a.a_div = a_div;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, n_pairs, 1, true, stream);
 }
@@ -299,7 +307,7 @@ extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group,
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr && tile_group != nullptr,
              "lp_linear_grouped: null operand");
   LP_REQUIRE(d->N > 0 && d->K > 0 && n_tiles >= 0, "lp_linear_grouped: bad problem N=%d K=%d tiles=%d", d->N, d->K, n_tiles);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_SILU_GATE, "lp_linear_grouped: bad epilogue %d", d->epi);
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear_grouped: bad epilogue %d", d->epi);
   LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear_grouped: the gated epilogue needs an even N");
   if (n_tiles == 0) return 0;
   LinArgs a;
@@ -307,7 +315,7 @@ extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group,
   a.W = reinterpret_cast<const bf16*>(d->W); a.ldw = d->ldw; a.w_batch = d->w_batch;   // w_batch = elements between groups
   a.C = d->C; a.ldc = d->ldc; a.c_batch = 0;
   a.M = n_tiles * LIN_BM; a.N = d->N; a.K = d->K;
-  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b;
+  a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = a_rows; a.tile_group = tile_group; a.z_group = nullptr; a.a_div = 1;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, 1, n_tiles, false, stream);
 }

@@ -1,10 +1,11 @@
 // leopard_b200 — glue kernels of models whose residual stream is kept in 32-bit floats.
 //
-//   lp_embed_rows_f32   x[r, :] = table[ids[r], :]  (bf16 table -> fp32 rows)
+//   lp_embed_rows_f32   x[r, :] = table[ids[r], :] * scale  (bf16 table -> fp32 rows)
 //   lp_rmsnorm_f32      y = x / sqrt(mean(x^2) + eps) * g over fp32 rows, eps inside the root; g is one number (gain_scalar), a vector
 //                       (gain_vec) or both.  The result is written as fp32 or bf16 (the operand of the next matrix product), or — with
 //                       `accum` — added to another fp32 matrix: the sandwich-norm residual update x <- x + norm(sublayer(x)) in one pass.
-//   lp_glu_f32          elementwise epilogues for matrix products that ran elsewhere: xIELU, silu(gate) * up.
+//   lp_glu_f32          elementwise epilogues for matrix products that ran elsewhere: xIELU, squared relu, silu(gate) * up.
+//   lp_axpy_f32         y <- y + alpha x, the residual update after such a product.
 //
 // One warp per row, statistics and normalisation in fp32; the row is read twice (the second read hits L1 / L2).
 #include "lp_host.h"
@@ -15,14 +16,14 @@ namespace lp {
 typedef __nv_bfloat16 bf16;
 
 __global__ void embed_rows_f32_kernel(const int* __restrict__ ids, int R, const bf16* __restrict__ table, long long ldt, int vocab,
-                                      float* __restrict__ out, long long ldo, int D) {
+                                      float scale, float* __restrict__ out, long long ldo, int D) {
   const int r = blockIdx.x;
   if (r >= R) return;
   int id = ids[r];
   if (id < 0 || id >= vocab) id = 0;   // the host validates ids; this only keeps a bad one inside the table
   const bf16* src = table + (long long)id * ldt;
   float* dst = out + (long long)r * ldo;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = __bfloat162float(src[c]);
+  for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = __bfloat162float(src[c]) * scale;
 }
 
 constexpr int NORM32_WARPS = 8;
@@ -67,20 +68,28 @@ __global__ void glu_kernel(const IT* __restrict__ in, long long ldi, OT* __restr
   const float z = ld32<IT>(in + (long long)m * ldi + n);
   float v;
   if (mode == LP_EPI_SILU_GATE) v = z / (1.0f + expf(-z)) * ld32<IT>(in + (long long)m * ldi + n + N);
+  else if (mode == LP_EPI_RELU2) v = fmaxf(z, 0.f) * fmaxf(z, 0.f);
   else v = z > 0.f ? a * z * z + 0.5f * z : b * (expm1f(z) - z) + 0.5f * z;
   st32(out + (long long)m * ldo + n, v);
+}
+
+__global__ void axpy_f32_kernel(float* __restrict__ y, long long ldy, const float* __restrict__ x, long long ldx, float alpha, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  y[(long long)m * ldy + n] = fmaf(alpha, x[(long long)m * ldx + n], y[(long long)m * ldy + n]);
 }
 
 }  // namespace lp
 
 using namespace lp;
 
-extern "C" int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float* out, long long ldo, int D,
-                                 void* stream_) {
+extern "C" int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float scale, float* out, long long ldo,
+                                 int D, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(ids != nullptr && table != nullptr && out != nullptr && R >= 0 && D > 0 && vocab > 0, "lp_embed_rows_f32: bad arguments");
   if (R == 0) return 0;
-  embed_rows_f32_kernel<<<R, 128, 0, stream>>>(ids, R, reinterpret_cast<const bf16*>(table), ldt, vocab, out, ldo, D);
+  embed_rows_f32_kernel<<<R, 128, 0, stream>>>(ids, R, reinterpret_cast<const bf16*>(table), ldt, vocab, scale, out, ldo, D);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -104,7 +113,7 @@ extern "C" int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out,
                           float a, float b, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(in != nullptr && out != nullptr && M >= 0 && N > 0, "lp_glu_f32: bad arguments");
-  LP_REQUIRE(mode == LP_EPI_XIELU || mode == LP_EPI_SILU_GATE, "lp_glu_f32: mode %d is not an activation", mode);
+  LP_REQUIRE(mode == LP_EPI_XIELU || mode == LP_EPI_SILU_GATE || mode == LP_EPI_RELU2, "lp_glu_f32: mode %d is not an activation", mode);
   if (M == 0) return 0;
   const unsigned grid = (unsigned)(((long long)M * N + 255) / 256);
   if (in_fp32 && out_fp32)
@@ -115,6 +124,16 @@ extern "C" int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out,
     glu_kernel<bf16, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b);
   else
     glu_kernel<bf16, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_axpy_f32(float* y, long long ldy, const float* x, long long ldx, float alpha, int M, int N, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(y != nullptr && x != nullptr && M >= 0 && N > 0, "lp_axpy_f32: bad arguments");
+  if (M == 0) return 0;
+  axpy_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(y, ldy, x, ldx, alpha, M, N);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -1,0 +1,446 @@
+// leopard_b200 — grouped-query attention with sliding-window visibility rules over a paged fp32 key / value cache.
+//
+// One family of kernels serves the windowed attention layers of the layer-list language models; what differs between designs is a
+// parameter of lp_window_attn_desc:
+//   visibility   window (tokens j with 0 <= i - j < window), keep_first (the request's first tokens stay visible), pool (every block
+//                of P tokens that lies wholly before the window is seen as ONE key / value, the mean of its cached rows)
+//   scores       scale, softcap * tanh(score / softcap), sink (softmax denominator + 1)
+//   projections  RMS norm of q and k per head or over the whole projection, rotation of the first rot_dims dimensions of q and k,
+//                optional rotation of the values by their own position with the head output turned back by the query's position
+//                (the weighted sum then depends on the distances i - j only)
+//
+//   lp_window_attn_prep   one CTA per row: sums of squares per head, then every (pair | single) element of q, k, v is normalised,
+//                         rotated and written: q in place, k and v into the request's page.
+//   lp_window_attn_pool   one CTA per completed block: the mean of its P cached rows -> the block's row in the pooled pool.
+//   lp_window_attn        one CTA per (row, group of QH query heads that share a key / value head).  Keys are walked 32 at a time by
+//                         each warp: every LANE owns one key and computes its QH scores (q in shared memory, the key row read once
+//                         for all QH heads), the warp agrees on the running maximum, then the 32 values are accumulated with the
+//                         lanes spread over vdim (weights broadcast through shared memory).  The CTA's warps take every W-th tile
+//                         and merge their (maximum, denominator, sum) triples at the end.  All of it in fp32.
+#include "lp_host.h"
+#include "../../include/leopard_b200.h"
+
+namespace lp {
+
+typedef __nv_bfloat16 bf16;
+
+struct WinArgs {
+  float* qkv; long long ld; int q_off, k_off, v_off;
+  int heads, kv_heads, dim, vdim;
+  int norm_mode; const float* q_gain; const float* k_gain; float eps;
+  const float* inv_freq; int rot_dims, rot_layout; float rot_mscale;
+  const float* v_inv_freq; int v_rot_dims, v_rot_layout;
+  float* cache; int page_size; const int* page_table; int max_pages;
+  float* pooled; const int* pooled_table; int max_pooled_pages; int pool;
+  int window, keep_first;
+  float scale, softcap; int sink;
+};
+
+__device__ __forceinline__ float* win_token_row(const WinArgs& a, int seq, int pos) {
+  const int page = a.page_table[(long long)seq * a.max_pages + pos / a.page_size];
+  return a.cache + ((long long)page * a.page_size + pos % a.page_size) * (long long)(a.kv_heads * (a.dim + a.vdim));
+}
+__device__ __forceinline__ float* win_block_row(const WinArgs& a, int seq, int block) {
+  const int page = a.pooled_table[(long long)seq * a.max_pooled_pages + block / a.page_size];
+  return a.pooled + ((long long)page * a.page_size + block % a.page_size) * (long long)(a.kv_heads * (a.dim + a.vdim));
+}
+
+// the two members of rotation pair i
+__device__ __forceinline__ void win_pair(int layout, int half, int i, int& d0, int& d1) {
+  if (layout == LP_ROT_INTERLEAVED) {
+    d0 = 2 * i;
+    d1 = 2 * i + 1;
+  } else {
+    d0 = i;
+    d1 = i + half;
+  }
+}
+
+// what a query at `pos` sees, as one index space: [kept first tokens | pooled blocks | window tokens]
+struct WinVisible {
+  int n_keep, n_blocks, lo, count;
+};
+__device__ __forceinline__ WinVisible win_visible(const WinArgs& a, int pos) {
+  WinVisible v;
+  v.lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  v.n_keep = a.keep_first < v.lo ? a.keep_first : v.lo;
+  if (v.n_keep < 0) v.n_keep = 0;
+  v.n_blocks = (a.pool > 0 && a.window > 0 && pos - a.window + 1 > 0) ? (pos - a.window + 1) / a.pool : 0;
+  v.count = v.n_keep + v.n_blocks + (pos - v.lo + 1);
+  return v;
+}
+__device__ __forceinline__ const float* win_visible_row(const WinArgs& a, const WinVisible& v, int seq, int t) {
+  if (t < v.n_keep) return win_token_row(a, seq, t);
+  if (t < v.n_keep + v.n_blocks) return win_block_row(a, seq, t - v.n_keep);
+  return win_token_row(a, seq, v.lo + (t - v.n_keep - v.n_blocks));
+}
+
+constexpr int WIN_PREP_THREADS = 128;
+__global__ void __launch_bounds__(WIN_PREP_THREADS)
+window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos) {
+  extern __shared__ float dyn_smem[];
+  float* s_ss = dyn_smem;      // [heads + kv_heads] sums of squares, then the two totals
+  const int r = blockIdx.x;
+  if (r >= R) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
+  const int seq = row_seq[r], pos = row_pos[r];
+  float* x = a.qkv + (long long)r * a.ld;
+  const int units = a.heads + a.kv_heads;
+  if (a.norm_mode != LP_QKNORM_NONE) {
+    for (int u = warp; u < units; u += n_warps) {
+      const float* src = u < a.heads ? x + a.q_off + u * a.dim : x + a.k_off + (u - a.heads) * a.dim;
+      float ss = 0.f;
+      for (int d = lane; d < a.dim; d += 32) ss = fmaf(src[d], src[d], ss);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_ss[u] = ss;
+    }
+    __syncthreads();
+    if (a.norm_mode == LP_QKNORM_FULL) {
+      if (tid == 0) {
+        float tq = 0.f, tk = 0.f;
+        for (int u = 0; u < a.heads; ++u) tq += s_ss[u];
+        for (int u = a.heads; u < units; ++u) tk += s_ss[u];
+        s_ss[units] = tq;
+        s_ss[units + 1] = tk;
+      }
+      __syncthreads();
+    }
+  }
+  float* crow = win_token_row(a, seq, pos);
+  // q and k: per head rot_dims / 2 pairs and dim - rot_dims single dimensions
+  const int half = a.rot_dims >> 1;
+  const int per = a.dim - half;
+  for (int it = tid; it < units * per; it += blockDim.x) {
+    const int u = it / per, e = it % per;
+    const bool is_q = u < a.heads;
+    const int hl = is_q ? u : u - a.heads;      // head inside its projection
+    const float* src = is_q ? x + a.q_off + hl * a.dim : x + a.k_off + hl * a.dim;
+    float* dst = is_q ? x + a.q_off + hl * a.dim : crow + hl * a.dim;
+    float rinv = 1.f;
+    const float* gain = nullptr;
+    if (a.norm_mode == LP_QKNORM_HEAD) {
+      rinv = 1.0f / sqrtf(s_ss[u] / (float)a.dim + a.eps);
+      gain = is_q ? a.q_gain : a.k_gain;
+    } else if (a.norm_mode == LP_QKNORM_FULL) {
+      rinv = 1.0f / sqrtf(s_ss[units + (is_q ? 0 : 1)] / (float)((is_q ? a.heads : a.kv_heads) * a.dim) + a.eps);
+      gain = (is_q ? a.q_gain : a.k_gain) + hl * a.dim;
+    }
+    if (e < half) {
+      int d0, d1;
+      win_pair(a.rot_layout, half, e, d0, d1);
+      float u0 = src[d0] * rinv, u1 = src[d1] * rinv;
+      if (gain != nullptr) {
+        u0 *= gain[d0];
+        u1 *= gain[d1];
+      }
+      float s, c;
+      sincosf((float)pos * a.inv_freq[e], &s, &c);
+      s *= a.rot_mscale;
+      c *= a.rot_mscale;
+      dst[d0] = u0 * c - u1 * s;
+      dst[d1] = u1 * c + u0 * s;
+    } else {
+      const int d = a.rot_dims + (e - half);
+      float v = src[d] * rinv;
+      if (gain != nullptr) v *= gain[d];
+      dst[d] = v;
+    }
+  }
+  // values: rotated over v_rot_dims by their own position when a table is given
+  const int vhalf = a.v_inv_freq != nullptr ? a.v_rot_dims >> 1 : 0;
+  const int vrot = 2 * vhalf;
+  const int vper = a.vdim - vhalf;
+  for (int it = tid; it < a.kv_heads * vper; it += blockDim.x) {
+    const int g = it / vper, e = it % vper;
+    const float* src = x + a.v_off + g * a.vdim;
+    float* dst = crow + a.kv_heads * a.dim + g * a.vdim;
+    if (e < vhalf) {
+      int d0, d1;
+      win_pair(a.v_rot_layout, vhalf, e, d0, d1);
+      float s, c;
+      sincosf((float)pos * a.v_inv_freq[e], &s, &c);
+      const float u0 = src[d0], u1 = src[d1];
+      dst[d0] = u0 * c - u1 * s;
+      dst[d1] = u1 * c + u0 * s;
+    } else {
+      const int d = vrot + (e - vhalf);
+      dst[d] = src[d];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+window_attn_pool_kernel(WinArgs a, int n_seqs, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0) {
+  const int s = blockIdx.x;
+  if (s >= n_seqs) return;
+  const int pos0 = seq_pos0[s], len = seq_row0[s + 1] - seq_row0[s];
+  const int b = pos0 / a.pool + blockIdx.y;
+  if (b >= (pos0 + len) / a.pool) return;      // block b is complete when its last token b P + P - 1 has been written
+  const int roww = a.kv_heads * (a.dim + a.vdim);
+  float* dst = win_block_row(a, s, b);
+  for (int c = threadIdx.x; c < roww; c += blockDim.x) {
+    float sum = 0.f;
+    for (int j = 0; j < a.pool; ++j) sum += win_token_row(a, s, b * a.pool + j)[c];
+    dst[c] = sum / (float)a.pool;
+  }
+}
+
+template <int QH, int NV>
+__global__ void __launch_bounds__(256)
+window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, void* __restrict__ out, long long ldo,
+                   int out_fp32) {
+  extern __shared__ float dyn_smem[];
+  const int r = blockIdx.x;
+  if (r >= R) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, W = blockDim.x >> 5;
+  const int ratio = a.heads / a.kv_heads, per_g = ratio / QH;
+  const int g = blockIdx.y / per_g, h0 = g * ratio + (blockIdx.y % per_g) * QH;
+  float* q_s = dyn_smem;                    // [QH][dim]
+  float* p_s = q_s + QH * a.dim;            // [W][QH][32] softmax weights of a warp's current tile
+  float* m_s = p_s + W * QH * 32;           // [W][QH]
+  float* d_s = m_s + W * QH;                // [W][QH]
+  float* o_s = d_s + W * QH;                // [W][QH][vdim]
+  float* f_s = o_s + W * QH * a.vdim;       // [QH][vdim] merged output before it is turned back
+  const int seq = row_seq[r], pos = row_pos[r];
+  const float* q = a.qkv + (long long)r * a.ld + a.q_off + (long long)h0 * a.dim;
+  for (int i = tid; i < QH * a.dim; i += blockDim.x) q_s[i] = q[i];
+  __syncthreads();
+  const WinVisible vis = win_visible(a, pos);
+  const int v_off = a.kv_heads * a.dim + g * a.vdim;
+  const bool vec = (a.dim % 4 == 0) && (a.vdim % 4 == 0);      // rows and head offsets are then 16-byte aligned
+  float mx[QH], den[QH], acc[QH][NV];
+#pragma unroll
+  for (int h = 0; h < QH; ++h) {
+    // the sink is a key of score 0 without a value: warp 0 starts from it
+    mx[h] = (a.sink && warp == 0) ? 0.f : -INFINITY;
+    den[h] = (a.sink && warp == 0) ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[h][i] = 0.f;
+  }
+  float* my_p = p_s + warp * QH * 32;
+  for (int t0 = warp * 32; t0 < vis.count; t0 += W * 32) {
+    const int t = t0 + lane;
+    const bool valid = t < vis.count;
+    float sc[QH];
+#pragma unroll
+    for (int h = 0; h < QH; ++h) sc[h] = 0.f;
+    if (valid) {
+      const float* kp = win_visible_row(a, vis, seq, t) + g * a.dim;
+      if (vec) {
+        for (int d = 0; d < a.dim; d += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
+#pragma unroll
+          for (int h = 0; h < QH; ++h) {
+            const float* qh = q_s + h * a.dim + d;
+            sc[h] = fmaf(qh[0], k4.x, sc[h]);
+            sc[h] = fmaf(qh[1], k4.y, sc[h]);
+            sc[h] = fmaf(qh[2], k4.z, sc[h]);
+            sc[h] = fmaf(qh[3], k4.w, sc[h]);
+          }
+        }
+      } else {
+        for (int d = 0; d < a.dim; ++d) {
+          const float kv = kp[d];
+#pragma unroll
+          for (int h = 0; h < QH; ++h) sc[h] = fmaf(q_s[h * a.dim + d], kv, sc[h]);
+        }
+      }
+    }
+    float corr[QH];
+#pragma unroll
+    for (int h = 0; h < QH; ++h) {
+      float s = sc[h] * a.scale;
+      if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+      if (!valid) s = -INFINITY;
+      float top = s;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+      const float mn = fmaxf(mx[h], top);      // finite: a tile holds at least one visible key
+      corr[h] = expf(mx[h] - mn);              // exp(-inf) = 0 on a warp's first tile
+      const float p = valid ? expf(s - mn) : 0.f;
+      float sum = p;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      den[h] = fmaf(den[h], corr[h], sum);
+      mx[h] = mn;
+      my_p[h * 32 + lane] = p;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[h][i] *= corr[h];
+    }
+    __syncwarp();
+    const int cnt = vis.count - t0 < 32 ? vis.count - t0 : 32;
+    for (int jj = 0; jj < cnt; ++jj) {
+      const float* vp = win_visible_row(a, vis, seq, t0 + jj) + v_off;
+      float pj[QH];
+#pragma unroll
+      for (int h = 0; h < QH; ++h) pj[h] = my_p[h * 32 + jj];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < a.vdim) {
+          const float vv = vp[c];
+#pragma unroll
+          for (int h = 0; h < QH; ++h) acc[h][i] = fmaf(pj[h], vv, acc[h][i]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int h = 0; h < QH; ++h) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < a.vdim) o_s[((long long)warp * QH + h) * a.vdim + c] = acc[h][i];
+    }
+    if (lane == 0) {
+      m_s[warp * QH + h] = mx[h];
+      d_s[warp * QH + h] = den[h];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < QH * a.vdim; i += blockDim.x) {
+    const int h = i / a.vdim, c = i % a.vdim;
+    float top = -INFINITY;
+    for (int w = 0; w < W; ++w)
+      if (d_s[w * QH + h] > 0.f) top = fmaxf(top, m_s[w * QH + h]);
+    float total = 0.f, v = 0.f;
+    for (int w = 0; w < W; ++w) {
+      if (d_s[w * QH + h] > 0.f) {      // a warp without keys contributes nothing
+        const float f = expf(m_s[w * QH + h] - top);
+        total = fmaf(d_s[w * QH + h], f, total);
+        v = fmaf(o_s[((long long)w * QH + h) * a.vdim + c], f, v);
+      }
+    }
+    f_s[i] = v / total;
+  }
+  __syncthreads();
+  // turn every head's output back by the query's position (pair i by -pos * v_inv_freq[i]) and store
+  const int vhalf = a.v_inv_freq != nullptr ? a.v_rot_dims >> 1 : 0;
+  for (int i = tid; i < QH * a.vdim; i += blockDim.x) {
+    const int h = i / a.vdim, c = i % a.vdim;
+    const float* o = f_s + h * a.vdim;
+    float v = o[c];
+    if (c < 2 * vhalf) {
+      int pair, partner;
+      bool first;
+      if (a.v_rot_layout == LP_ROT_INTERLEAVED) {
+        pair = c >> 1;
+        first = (c & 1) == 0;
+        partner = first ? c + 1 : c - 1;
+      } else {
+        first = c < vhalf;
+        pair = first ? c : c - vhalf;
+        partner = first ? c + vhalf : c - vhalf;
+      }
+      float s, cs;
+      sincosf((float)pos * a.v_inv_freq[pair], &s, &cs);
+      // rotation by the negative angle: (u, v) -> (u cos + v sin, v cos - u sin)
+      v = first ? o[c] * cs + o[partner] * s : o[c] * cs - o[partner] * s;
+    }
+    const long long at = (long long)r * ldo + (long long)(h0 + h) * a.vdim + c;
+    if (out_fp32) reinterpret_cast<float*>(out)[at] = v;
+    else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16(v);
+  }
+}
+
+static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
+  LP_REQUIRE(d != nullptr && d->cache != nullptr && d->page_table != nullptr, "lp_window_attn: null operand");
+  LP_REQUIRE(!need_q || d->qkv != nullptr, "lp_window_attn: null projection");
+  LP_REQUIRE(d->heads > 0 && d->kv_heads > 0 && d->heads % d->kv_heads == 0 && d->dim > 0 && d->vdim > 0,
+             "lp_window_attn: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d", d->heads, d->kv_heads, d->dim, d->vdim);
+  LP_REQUIRE(d->page_size > 0 && d->max_pages > 0, "lp_window_attn: bad page table");
+  LP_REQUIRE(d->rot_dims >= 0 && d->rot_dims <= d->dim && d->rot_dims % 2 == 0, "lp_window_attn: rot_dims=%d must be even and <= dim=%d",
+             d->rot_dims, d->dim);
+  LP_REQUIRE(d->rot_dims == 0 || d->inv_freq != nullptr, "lp_window_attn: rotation without a frequency table");
+  LP_REQUIRE(d->v_inv_freq == nullptr || (d->v_rot_dims >= 0 && d->v_rot_dims <= d->vdim && d->v_rot_dims % 2 == 0),
+             "lp_window_attn: v_rot_dims=%d must be even and <= vdim=%d", d->v_rot_dims, d->vdim);
+  LP_REQUIRE(d->norm_mode >= LP_QKNORM_NONE && d->norm_mode <= LP_QKNORM_FULL, "lp_window_attn: bad norm mode %d", d->norm_mode);
+  LP_REQUIRE(d->norm_mode == LP_QKNORM_NONE || (d->q_gain != nullptr && d->k_gain != nullptr), "lp_window_attn: norm without gains");
+  LP_REQUIRE(d->pool >= 0 && (d->pool == 0 || (d->pooled != nullptr && d->pooled_table != nullptr && d->max_pooled_pages > 0)),
+             "lp_window_attn: pooled blocks without their pool");
+  LP_REQUIRE(d->keep_first >= 0, "lp_window_attn: keep_first < 0");
+  a.qkv = d->qkv; a.ld = d->ld; a.q_off = d->q_off; a.k_off = d->k_off; a.v_off = d->v_off;
+  a.heads = d->heads; a.kv_heads = d->kv_heads; a.dim = d->dim; a.vdim = d->vdim;
+  a.norm_mode = d->norm_mode; a.q_gain = d->q_gain; a.k_gain = d->k_gain; a.eps = d->eps;
+  a.inv_freq = d->inv_freq; a.rot_dims = d->rot_dims; a.rot_layout = d->rot_layout; a.rot_mscale = d->rot_mscale;
+  a.v_inv_freq = d->v_inv_freq; a.v_rot_dims = d->v_rot_dims; a.v_rot_layout = d->v_rot_layout;
+  a.cache = d->cache; a.page_size = d->page_size; a.page_table = d->page_table; a.max_pages = d->max_pages;
+  a.pooled = d->pooled; a.pooled_table = d->pooled_table; a.max_pooled_pages = d->max_pooled_pages; a.pool = d->pool;
+  a.window = d->window; a.keep_first = d->keep_first;
+  a.scale = d->scale; a.softcap = d->softcap; a.sink = d->sink;
+  return 0;
+}
+
+constexpr int WIN_MAX_DIM = 256;
+constexpr int WIN_SPLIT_ROWS = 16;      // up to this many rows (decoding) a CTA has 8 warps, else 4
+
+static size_t win_smem_floats(int qh, int w, int dim, int vdim) {
+  return (size_t)qh * dim + (size_t)w * qh * 32 + 2 * (size_t)w * qh + (size_t)w * qh * vdim + (size_t)qh * vdim;
+}
+
+template <int QH>
+static int launch_window_attn(const WinArgs& a, int R, const int* row_seq, const int* row_pos, void* out, long long ldo, int out_fp32,
+                              cudaStream_t stream) {
+  int warps = R <= WIN_SPLIT_ROWS ? 8 : 4;
+  while (warps > 1 && win_smem_floats(QH, warps, a.dim, a.vdim) * sizeof(float) > 48 * 1024) warps >>= 1;
+  const size_t smem = win_smem_floats(QH, warps, a.dim, a.vdim) * sizeof(float);
+  LP_REQUIRE(smem <= 48 * 1024, "lp_window_attn: dim=%d vdim=%d do not fit shared memory", a.dim, a.vdim);
+  const dim3 grid(R, a.kv_heads * (a.heads / a.kv_heads / QH));
+  const int nv = (a.vdim + 31) / 32;
+  if (nv <= 1) window_attn_kernel<QH, 1><<<grid, warps * 32, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  else if (nv <= 2) window_attn_kernel<QH, 2><<<grid, warps * 32, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  else if (nv <= 4) window_attn_kernel<QH, 4><<<grid, warps * 32, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  else window_attn_kernel<QH, 8><<<grid, warps * 32, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace lp
+
+using namespace lp;
+
+extern "C" int lp_window_attn_prep(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  WinArgs a;
+  if (int rc = fill_win(a, d, true)) return rc;
+  LP_REQUIRE(row_seq != nullptr && row_pos != nullptr, "lp_window_attn_prep: null operand");
+  if (R <= 0) return 0;
+  const size_t smem = (size_t)(d->heads + d->kv_heads + 2) * sizeof(float);
+  LP_REQUIRE(smem <= 48 * 1024, "lp_window_attn_prep: too many heads");
+  window_attn_prep_kernel<<<R, WIN_PREP_THREADS, smem, stream>>>(a, R, row_seq, row_pos);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_window_attn_pool(const lp_window_attn_desc* d, int n_seqs, const int* seq_row0, const int* seq_pos0, int max_new_blocks,
+                                   void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  WinArgs a;
+  if (int rc = fill_win(a, d, false)) return rc;
+  LP_REQUIRE(d->pool > 0 && seq_row0 != nullptr && seq_pos0 != nullptr, "lp_window_attn_pool: no pooled blocks in this description");
+  if (n_seqs <= 0 || max_new_blocks <= 0) return 0;
+  LP_REQUIRE(max_new_blocks <= 65535, "lp_window_attn_pool: %d blocks per request in one step", max_new_blocks);
+  window_attn_pool_kernel<<<dim3(n_seqs, max_new_blocks), 128, 0, stream>>>(a, n_seqs, seq_row0, seq_pos0);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_window_attn(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
+                              int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  WinArgs a;
+  if (int rc = fill_win(a, d, true)) return rc;
+  LP_REQUIRE(out != nullptr && row_seq != nullptr && row_pos != nullptr, "lp_window_attn: null operand");
+  LP_REQUIRE(d->dim <= WIN_MAX_DIM && d->vdim <= WIN_MAX_DIM, "lp_window_attn: dim=%d / vdim=%d > %d is not instantiated", d->dim, d->vdim,
+             WIN_MAX_DIM);
+  if (R <= 0) return 0;
+  const int ratio = d->heads / d->kv_heads;
+  if (ratio % 4 == 0) return launch_window_attn<4>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  if (ratio % 2 == 0) return launch_window_attn<2>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  return launch_window_attn<1>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+}

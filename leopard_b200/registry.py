@@ -45,12 +45,18 @@ def _zudalorn(path, **kw):
     return zudalorn.load(path, **kw)
 
 
+def _ronelorn(path, **kw):
+    from . import ronelorn
+    return ronelorn.load(path, **kw)
+
+
 def _llava(path, **kw):
     from .hf import myLlavaForConditionalGeneration
     return myLlavaForConditionalGeneration.from_pretrained(path, **kw)
 
 
 register("Zudalorn", _zudalorn)
+register("Ronelorn", _ronelorn)
 register("LlavaForConditionalGeneration", _llava)
 register("myLlavaForConditionalGeneration", _llava)
 register("llava", _llava)

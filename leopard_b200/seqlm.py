@@ -1,7 +1,8 @@
 """Decoder-only language models described as a LIST OF LAYERS, on the 32-bit residual-stream kernels.
 
-A model is a `SeqLMConfig`: vocabulary, width, norm epsilon and a tuple of `LayerConfig`s, each naming its sequence mixer
-(`RetentionConfig` or `LatentAttentionConfig`) and its feed-forward (`DenseFFConfig`, `MoEConfig` or none).  Every mechanism is a
+A model is a `SeqLMConfig`: vocabulary, width, norm epsilon and style, and a tuple of `LayerConfig`s, each naming its sequence mixer
+(`RetentionConfig`, `LatentAttentionConfig`, `WindowAttentionConfig` or `MinGRUConfig`) and its feed-forward (`DenseFFConfig`,
+`MoEConfig` or none); a layer may run on another layer's weights with a cache or state of its own.  Every mechanism is a
 separate native entry point with its constants as arguments (include/leopard_b200.h, "32-BIT RESIDUAL-STREAM MODELS"), so another
 design is another list.  The residual stream, norms, routers, rotary angles, attention scores and recurrent state are fp32; matrix
 products take bf16 weights and, in the serving precision, bf16 activations with fp32 accumulation ("bfloat16"), or fp32 activations
@@ -46,11 +47,17 @@ class YarnScaling:
 
 
 @dataclass(frozen=True)
+class LinearScaling:
+    """Position interpolation: every frequency is divided by `factor`."""
+    factor: float
+
+
+@dataclass(frozen=True)
 class RotaryConfig:
     dims: int                      # leading dimensions of a head that are rotated
     base: float
     layout: str = "half"           # "half": i pairs with i + dims/2; "interleaved": 2i pairs with 2i + 1
-    scaling: Optional[YarnScaling] = None
+    scaling: Union[YarnScaling, LinearScaling, None] = None
 
 
 def rotary_table(rot: RotaryConfig) -> Tuple[torch.Tensor, float]:
@@ -62,7 +69,9 @@ def rotary_table(rot: RotaryConfig) -> Tuple[torch.Tensor, float]:
     f = rot.base ** (-2.0 * i / rot.dims) if n else np.zeros(0)
     mag = 1.0
     s = rot.scaling
-    if s is not None:
+    if isinstance(s, LinearScaling):
+        f = f / s.factor
+    elif s is not None:
         def pair_index(turns):      # the (fractional) pair index whose wavelength fits `turns` times into the original context
             return rot.dims * math.log(s.original / (2 * math.pi * turns)) / (2 * math.log(rot.base))
         lo = max(math.floor(pair_index(s.fast)), 0)
@@ -99,8 +108,33 @@ class LatentAttentionConfig:
 
 
 @dataclass(frozen=True)
+class WindowAttentionConfig:
+    """Grouped-query softmax attention over cached keys and values with sliding-window visibility (csrc/lp_winattn.cu)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: RotaryConfig
+    qk_norm: str = "none"          # RMS norm of q and k before rotation: "head" (per head, gain [dim]), "full" (whole projection), "none"
+    window: Optional[int] = None   # position i sees j with 0 <= i - j < window; None: every earlier position
+    keep_first: int = 0            # the first tokens of a request stay visible beyond the window
+    pool: int = 0                  # > 0: blocks of this many tokens wholly before the window are seen as one mean key / value
+    softcap: float = 0.0           # > 0: score <- softcap tanh(score / softcap)
+    sink: bool = False             # one added to the softmax denominator
+    value_rot: Optional[RotaryConfig] = None   # values rotated by their position, outputs turned back by the query's
+
+
+@dataclass(frozen=True)
+class MinGRUConfig:
+    """Gated recurrence whose gates read only the current token (csrc/lp_mingru.cu)."""
+    width: int
+
+
+@dataclass(frozen=True)
 class DenseFFConfig:
     ff: int
+    act: str = "xielu"             # "xielu" (two learned constants in mlp.act) or "relu2" (the square of relu)
 
 
 @dataclass(frozen=True)
@@ -115,8 +149,9 @@ class MoEConfig:
 
 @dataclass(frozen=True)
 class LayerConfig:
-    mixer: Union[RetentionConfig, LatentAttentionConfig]
+    mixer: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig]
     ff: Union[DenseFFConfig, MoEConfig, None]
+    weights_of: Optional[int] = None   # run on that layer's tensors (mixer, feed-forward, norms); cache and state stay this layer's own
 
 
 @dataclass(frozen=True)
@@ -126,6 +161,11 @@ class SeqLMConfig:
     width: int
     eps: float
     layers: Tuple[LayerConfig, ...]
+    # "sandwich": x <- x + norm_b(sublayer(norm_a(x))), every norm with ONE gain; "pre": x <- x + residual_mult * sublayer(norm(x)),
+    # the norm's gain a vector stored around zero (x / rms * (1 + w))
+    norm: str = "sandwich"
+    residual_mult: float = 1.0
+    embed_scale: float = 1.0
 
 
 def softplus(x: float) -> float:
@@ -153,17 +193,54 @@ class SeqLMWeights:
         def num(layer, key):
             return float(w(layer, key).float().reshape(-1)[0])
 
+        def vec(t):
+            return t.float().contiguous().to(dev)
+
+        def one_plus(layer, key):           # a gain stored around zero
+            return (1.0 + w(layer, key, (cfg.width,)).float()).contiguous().to(dev)
+
+        if cfg.norm not in ("sandwich", "pre"):
+            raise ValueError(f"unknown norm style {cfg.norm!r}")
+        pre = cfg.norm == "pre"
         D = cfg.width
         self.embed = mat(w(None, "embed", (cfg.vocab, D)))
         self.head = mat(w(None, "head", (cfg.vocab, D)))
-        self.final_gain = num(None, "final.norm")
+        self.final_gain = one_plus(None, "final.norm") if pre else num(None, "final.norm")
         self.layers: List[Dict[str, object]] = []
         for i, lc in enumerate(cfg.layers):
-            lw: Dict[str, object] = {k: num(i, k) for k in ("norm1", "norm1b")}
+            if lc.weights_of is not None:
+                j = lc.weights_of
+                if not 0 <= j < i or cfg.layers[j].weights_of is not None:
+                    raise ValueError(f"layer {i}: weights_of = {j} must name an earlier layer that has tensors of its own")
+                if (cfg.layers[j].mixer, cfg.layers[j].ff) != (lc.mixer, lc.ff):
+                    raise ValueError(f"layer {i} differs from layer {j}, whose weights it uses")
+                self.layers.append(self.layers[j])
+                continue
+            lw: Dict[str, object] = {"norm1": one_plus(i, "norm1")} if pre else {k: num(i, k) for k in ("norm1", "norm1b")}
             m = lc.mixer
-            inv_freq, mag = rotary_table(m.rot)
-            lw["inv_freq"], lw["rot_mag"] = inv_freq.to(dev), mag
-            if isinstance(m, RetentionConfig):
+            if not isinstance(m, MinGRUConfig):
+                inv_freq, mag = rotary_table(m.rot)
+                lw["inv_freq"], lw["rot_mag"] = inv_freq.to(dev), mag
+            if isinstance(m, MinGRUConfig):
+                lw["w_zxg"] = mat(torch.cat([w(i, "mix.z", (m.width, D)), w(i, "mix.x", (m.width, D)), w(i, "mix.g", (m.width, D))], 0))
+                lw["z_bias"], lw["x_bias"] = vec(w(i, "mix.z.b", (m.width,))), vec(w(i, "mix.x.b", (m.width,)))
+                lw["w_o"] = mat(w(i, "mix.o", (D, m.width)))
+            elif isinstance(m, WindowAttentionConfig):
+                if m.heads % m.kv_heads:
+                    raise ValueError(f"layer {i}: {m.heads} query heads over {m.kv_heads} key / value heads")
+                lw["w_qkv"] = mat(torch.cat([w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.kv_heads * m.dim, D)),
+                                             w(i, "mix.v", (m.kv_heads * m.vdim, D))], 0))
+                if m.qk_norm == "head":
+                    lw["q_gain"], lw["k_gain"] = vec(w(i, "mix.q.norm", (m.dim,))), vec(w(i, "mix.k.norm", (m.dim,)))
+                elif m.qk_norm == "full":
+                    lw["q_gain"] = vec(w(i, "mix.q.norm", (m.heads * m.dim,)))
+                    lw["k_gain"] = vec(w(i, "mix.k.norm", (m.kv_heads * m.dim,)))
+                elif m.qk_norm != "none":
+                    raise ValueError(f"layer {i}: unknown query / key norm {m.qk_norm!r}")
+                if m.value_rot is not None:
+                    lw["v_inv_freq"] = rotary_table(m.value_rot)[0].to(dev)
+                lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
+            elif isinstance(m, RetentionConfig):
                 if len(m.decay) != m.heads:
                     raise ValueError(f"layer {i}: {len(m.decay)} decays for {m.heads} heads")
                 lw["w_qkvg"] = mat(torch.cat([w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.heads * m.dim, D)),
@@ -180,12 +257,15 @@ class SeqLMWeights:
                 lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
             f = lc.ff
             if f is not None:
-                lw.update({k: num(i, k) for k in ("norm2", "norm2b")})
+                lw.update({"norm2": one_plus(i, "norm2")} if pre else {k: num(i, k) for k in ("norm2", "norm2b")})
             if isinstance(f, DenseFFConfig):
                 lw["w_up"] = mat(w(i, "mlp.up", (f.ff, D)))
                 lw["w_down"] = mat(w(i, "mlp.down", (D, f.ff)))
-                act = w(i, "mlp.act", (2,)).float()
-                lw["act_a"], lw["act_b"] = softplus(float(act[0])), 0.5 + softplus(float(act[1]))
+                if f.act == "xielu":
+                    act = w(i, "mlp.act", (2,)).float()
+                    lw["act_a"], lw["act_b"] = softplus(float(act[0])), 0.5 + softplus(float(act[1]))
+                elif f.act != "relu2":
+                    raise ValueError(f"layer {i}: unknown activation {f.act!r}")
             elif isinstance(f, MoEConfig):
                 lw["w_router"] = mat(w(i, "mlp.router", (f.experts, D)))
                 try:
@@ -241,12 +321,22 @@ class _Batch:
             raise ValueError("token id outside the vocabulary")
         row_seq = np.repeat(np.arange(n, dtype=np.int32), lens)
         row_pos = np.concatenate([np.arange(p, p + ln, dtype=np.int32) for p, ln in zip(pos0, lens)])
-        max_pages = max([len(s.pages) for s in seqs] + [1])
-        if self.decode:
-            max_pages = -(-max_pages // PAGE_TABLE_STEP) * PAGE_TABLE_STEP      # the width is a launch argument: change it rarely
-        table = np.full((n, max_pages), -1, np.int32)
-        for i, s in enumerate(seqs):
-            table[i, : len(s.pages)] = s.pages
+        def page_table(lists):
+            width = max([len(p) for p in lists] + [1])
+            if self.decode:
+                width = -(-width // PAGE_TABLE_STEP) * PAGE_TABLE_STEP      # the width is a launch argument: change it rarely
+            t = np.full((n, width), -1, np.int32)
+            for i, p in enumerate(lists):
+                t[i, : len(p)] = p
+            return t, width
+        table, max_pages = page_table([s.pages for s in seqs])
+        # summary streams (one per block size): their page tables, and the most blocks one request completes in this step
+        sum_tables, self.summary_width, self.summary_new = [], [], []
+        for k, every in enumerate(cache.summary_every):
+            t, width = page_table([s.summary_pages[k] for s in seqs])
+            sum_tables.append(t.reshape(-1))
+            self.summary_width.append(width)
+            self.summary_new.append(max((s.length + ln) // every - s.length // every for s, ln in zip(seqs, lens)))
         ch = _lib.RETENTION_CHUNK
         c_seq, c_row0, c_len, seq_c0 = [], [], [], [0]
         for i, ln in enumerate(lens):
@@ -263,10 +353,10 @@ class _Batch:
                 raise ValueError(f"request {e.key!r}: a wanted index is outside its tokens")
         self.n_want = len(want)
         parts = [tokens.astype(np.int32), row_seq, row_pos, row0, pos0, slot, table.reshape(-1), np.asarray(c_seq, np.int32),
-                 np.asarray(c_row0, np.int32), np.asarray(c_len, np.int32), np.asarray(seq_c0, np.int32)]
+                 np.asarray(c_row0, np.int32), np.asarray(c_len, np.int32), np.asarray(seq_c0, np.int32)] + sum_tables
         tables = torch.from_numpy(np.concatenate(parts).astype(np.int32))
         want_t = torch.from_numpy(np.asarray(want, np.int32))
-        self.layout = (n, max_pages) if self.decode else None      # fixes the size of every table of a decode batch
+        self.layout = (n, max_pages, *self.summary_width) if self.decode else None      # fixes the size of every table of a decode batch
         if eng.device.type == "cuda":
             host = tables.pin_memory()
             if static is not None and self.decode:
@@ -283,7 +373,8 @@ class _Batch:
             views.append(tables[o:o + len(p)])
             o += len(p)
         (self.tokens, self.row_seq, self.row_pos, self.seq_row0, self.seq_pos0, self.seq_slot, self.page_table, self.chunk_seq,
-         self.chunk_row0, self.chunk_len, self.seq_chunk0) = views
+         self.chunk_row0, self.chunk_len, self.seq_chunk0) = views[:11]
+        self.summary_table = views[11:]
         self.want_rows = want_t
         self._tables = tables
 
@@ -302,17 +393,40 @@ class SeqLMEngine:
         self.L = lib
         self.dtype = dtype
         self.act = BF16 if dtype == "bfloat16" else F32
-        lat = [lc.mixer for lc in cfg.layers if isinstance(lc.mixer, LatentAttentionConfig)]
-        ret = [lc.mixer for lc in cfg.layers if isinstance(lc.mixer, RetentionConfig)]
-        window = None if any(m.window is None or m.window <= 0 for m in lat) else max([m.window for m in lat], default=None)
-        self.cache = SequenceCache([m.kv_rank + m.rot_dim for m in lat], [(m.heads, m.dim, m.vdim) for m in ret], window, self.device,
-                                   max_tokens=max_tokens, page_size=page_size, max_seqs=max_seqs)
-        self._cache_index, self._state_index, a, b = [], [], 0, 0
+        # what every layer keeps per request: rows of a paged cache (attention), rows of a summary pool (pooled blocks), a state
+        rows, states, summaries, looks, keep = [], [], [], [], 0
+        self._cache_index, self._state_index, self._summary_index = [], [], []
         for lc in cfg.layers:
-            is_lat = isinstance(lc.mixer, LatentAttentionConfig)
-            self._cache_index.append(a if is_lat else -1)
-            self._state_index.append(-1 if is_lat else b)
-            a, b = a + is_lat, b + (not is_lat)
+            m = lc.mixer
+            ci = si = pi = -1
+            if isinstance(m, LatentAttentionConfig):
+                ci = len(rows)
+                rows.append(m.kv_rank + m.rot_dim)
+                looks.append(m.window if m.window and m.window > 0 else None)
+            elif isinstance(m, WindowAttentionConfig):
+                ci = len(rows)
+                rows.append(m.kv_heads * (m.dim + m.vdim))
+                windowed = bool(m.window and m.window > 0)
+                if windowed and m.pool > 0:
+                    pi = len(summaries)
+                    summaries.append((m.kv_heads * (m.dim + m.vdim), m.pool))
+                # a pooled layer reads a block's tokens once more when the block is complete
+                looks.append(max(m.window, m.pool) if windowed else None)
+                keep = max(keep, m.keep_first if windowed else 0)
+            elif isinstance(m, RetentionConfig):
+                si = len(states)
+                states.append((m.heads, m.dim, m.vdim))
+            elif isinstance(m, MinGRUConfig):
+                si = len(states)
+                states.append((m.width,))
+            else:
+                raise TypeError(f"unknown mixer {type(m).__name__}")
+            self._cache_index.append(ci)
+            self._state_index.append(si)
+            self._summary_index.append(pi)
+        window = None if any(x is None for x in looks) else max(looks, default=None)
+        self.cache = SequenceCache(rows, states, window, self.device, max_tokens=max_tokens, page_size=page_size, max_seqs=max_seqs,
+                                   keep_first=keep, summaries=summaries)
         self.tile_rows = int(self.L.lp_linear_tile_rows())
         # large bf16 products of the serving precision go to the tcgen05 GEMM when the library has it (the native ones do)
         self.tensor_core_rows = TENSOR_CORE_MIN_ROWS if dtype == "bfloat16" and hasattr(self.L, "lp_gemm_bf16") else None
@@ -341,11 +455,23 @@ class SeqLMEngine:
                 and N % 8 == 0 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0, out=None):
-        """out[M, N'] = epi(a[M, K] @ w[N, K].T)."""
+    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0, out=None, into=None):
+        """out[M, N'] = epi(a[M, K] @ w[N, K].T); with into = (x fp32 [M, N'], m): x <- x + m * epi(...) and x is returned."""
         M, K = a.shape
         N = w.shape[0]
         n_out = N // 2 if epi == _lib.EPI_SILU_GATE else N
+        if into is not None:
+            x, mult = into
+            if self._on_tensor_cores(a, w, M, N, K):
+                y = self.linear(a, w, F32, epi, epi_a, epi_b)
+                rc = self.L.lp_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0), float(mult), M, n_out, self._stream())
+                self._check(rc, "lp_axpy_f32")
+                return x
+            d = _lib.LinearDesc(A=_lib.ptr(a), lda=a.stride(0), a_batch=0, a_fp32=int(a.dtype == F32), W=_lib.ptr(w), ldw=w.stride(0),
+                                w_batch=0, C=_lib.ptr(x), ldc=x.stride(0), c_batch=0, c_fp32=1, M=M, N=N, K=K, batch=1, epi=epi,
+                                epi_a=epi_a, epi_b=epi_b, c_accum=1, c_scale=float(mult))
+            self._check(self.L.lp_linear(C.byref(d), self._stream()), "lp_linear")
+            return x
         if out is None:
             out = self._empty((M, n_out), out_dtype)
         if self._on_tensor_cores(a, w, M, N, K) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
@@ -373,18 +499,20 @@ class SeqLMEngine:
         self._check(self.L.lp_linear(C.byref(d), self._stream()), "lp_linear")
         return out
 
-    def norm(self, x: torch.Tensor, gain: float, out_dtype=None, accum: Optional[torch.Tensor] = None):
-        """RMS norm with one gain for all coordinates; `accum`: add the result to it instead of returning it."""
+    def norm(self, x: torch.Tensor, gain, out_dtype=None, accum: Optional[torch.Tensor] = None):
+        """RMS norm with one gain for all coordinates (a float) or one per coordinate (an fp32 device vector); `accum`: add the
+        result to it instead of returning it."""
         M, D = x.shape
         out = None if accum is not None else self._empty((M, D), out_dtype)
-        rc = self.L.lp_rmsnorm_f32(_lib.ptr(x), x.stride(0), M, D, gain, None, self.cfg.eps, _lib.ptr(out),
+        scalar, vector = (1.0, gain) if isinstance(gain, torch.Tensor) else (gain, None)
+        rc = self.L.lp_rmsnorm_f32(_lib.ptr(x), x.stride(0), M, D, scalar, _lib.ptr(vector), self.cfg.eps, _lib.ptr(out),
                                    out.stride(0) if out is not None else 0, int(out is not None and out.dtype == F32), _lib.ptr(accum),
                                    accum.stride(0) if accum is not None else 0, self._stream())
         self._check(rc, "lp_rmsnorm_f32")
         return out
 
     # ------------------------------------------------------------------ mixers
-    def _retention(self, li: int, m: RetentionConfig, lw, h: torch.Tensor, b: _Batch) -> torch.Tensor:
+    def _retention(self, li: int, m: RetentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
         qkvg = self.linear(h, lw["w_qkvg"], F32)
         hd, hv = m.heads * m.dim, m.heads * m.vdim
         out = self._empty((b.R, hv), self.act)
@@ -404,9 +532,9 @@ class SeqLMEngine:
                                              _lib.ptr(b.seq_chunk0), _lib.ptr(b.chunk_seq), _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len),
                                              _lib.ptr(ws), nbytes, self._stream())
             self._check(rc, "lp_retention_prefill")
-        return self.linear(out, lw["w_o"], F32)
+        return self.linear(out, lw["w_o"], F32, into=into)
 
-    def _latent(self, li: int, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch) -> torch.Tensor:
+    def _latent(self, li: int, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
         per = m.dim + m.rot_dim
         qd = self.linear(h, lw["w_qdkv"], F32)
         q, dkv = qd[:, : m.heads * per], qd[:, m.heads * per:]
@@ -426,12 +554,77 @@ class SeqLMEngine:
         self._check(rc, "lp_latent_attend")
         o = self._empty((b.R, m.heads * m.vdim), self.act)
         self.linear_heads(lat, m.kv_rank, lw["w_uv"].view(m.heads, m.vdim, m.kv_rank), o, m.vdim)
-        return self.linear(o, lw["w_o"], F32)
+        return self.linear(o, lw["w_o"], F32, into=into)
+
+    def _window_attention(self, li: int, m: WindowAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        qkv = self.linear(h, lw["w_qkv"], F32)
+        hq, hk = m.heads * m.dim, m.kv_heads * m.dim
+        cache = self.cache
+        pool = cache.pools[self._cache_index[li]]
+        windowed = bool(m.window and m.window > 0)
+        pi = self._summary_index[li]
+        stream = cache.summary_index[pi][0] if pi >= 0 else -1
+        layouts = {"half": _lib.ROT_HALF, "interleaved": _lib.ROT_INTERLEAVED}
+        vr = m.value_rot
+        d = _lib.WindowAttnDesc(
+            qkv=_lib.ptr(qkv), ld=qkv.stride(0), q_off=0, k_off=hq, v_off=hq + hk, heads=m.heads, kv_heads=m.kv_heads, dim=m.dim,
+            vdim=m.vdim, norm_mode={"none": _lib.QKNORM_NONE, "head": _lib.QKNORM_HEAD, "full": _lib.QKNORM_FULL}[m.qk_norm],
+            q_gain=_lib.ptr(lw.get("q_gain")), k_gain=_lib.ptr(lw.get("k_gain")), eps=self.cfg.eps, inv_freq=_lib.ptr(lw["inv_freq"]),
+            rot_dims=m.rot.dims, rot_layout=layouts[m.rot.layout], rot_mscale=lw["rot_mag"],
+            v_inv_freq=_lib.ptr(lw.get("v_inv_freq")), v_rot_dims=vr.dims if vr else 0, v_rot_layout=layouts[vr.layout] if vr else 0,
+            cache=_lib.ptr(pool), page_size=cache.page_size, page_table=_lib.ptr(b.page_table), max_pages=b.max_pages,
+            pooled=_lib.ptr(cache.summary_pool(pi)) if pi >= 0 else None,
+            pooled_table=_lib.ptr(b.summary_table[stream]) if pi >= 0 else None,
+            max_pooled_pages=b.summary_width[stream] if pi >= 0 else 0, pool=m.pool if pi >= 0 else 0,
+            window=m.window if windowed else 0, keep_first=m.keep_first if windowed else 0, scale=m.scale, softcap=m.softcap,
+            sink=int(m.sink))
+        st = self._stream()
+        self._check(self.L.lp_window_attn_prep(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), st), "lp_window_attn_prep")
+        if pi >= 0:
+            # a one-token step completes at most one block per request; the launch shape of a decode step must not depend on positions
+            new = 1 if b.decode else b.summary_new[stream]
+            rc = self.L.lp_window_attn_pool(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), new, st)
+            self._check(rc, "lp_window_attn_pool")
+        o = self._empty((b.R, m.heads * m.vdim), self.act)
+        rc = self.L.lp_window_attn(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0), int(o.dtype == F32), st)
+        self._check(rc, "lp_window_attn")
+        return self.linear(o, lw["w_o"], F32, into=into)
+
+    def _mingru(self, li: int, m: MinGRUConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        zxg = self.linear(h, lw["w_zxg"], F32)
+        out = self._empty((b.R, m.width), self.act)
+        state = self.cache.states[self._state_index[li]]
+        d = _lib.MinGRUDesc(zxg=_lib.ptr(zxg), ld=zxg.stride(0), z_off=0, x_off=m.width, g_off=2 * m.width, width=m.width,
+                            z_bias=_lib.ptr(lw["z_bias"]), x_bias=_lib.ptr(lw["x_bias"]), state=_lib.ptr(state), slot_stride=state.stride(0),
+                            out=_lib.ptr(out), ldo=out.stride(0), out_fp32=int(out.dtype == F32))
+        if b.decode:
+            rc = self.L.lp_mingru_decode(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), _lib.ptr(b.seq_slot), self._stream())
+            self._check(rc, "lp_mingru_decode")
+        else:
+            nbytes = int(self.L.lp_mingru_workspace_bytes(b.n_chunks, m.width))
+            ws = self._empty((nbytes // 4,), F32)
+            rc = self.L.lp_mingru_prefill(C.byref(d), b.n, b.n_chunks, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), _lib.ptr(b.seq_slot),
+                                          _lib.ptr(b.seq_chunk0), _lib.ptr(b.chunk_seq), _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len),
+                                          _lib.ptr(ws), nbytes, self._stream())
+            self._check(rc, "lp_mingru_prefill")
+        return self.linear(out, lw["w_o"], F32, into=into)
+
+    def _mix(self, li: int, m, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        if isinstance(m, RetentionConfig):
+            return self._retention(li, m, lw, h, b, into)
+        if isinstance(m, LatentAttentionConfig):
+            return self._latent(li, m, lw, h, b, into)
+        if isinstance(m, WindowAttentionConfig):
+            return self._window_attention(li, m, lw, h, b, into)
+        return self._mingru(li, m, lw, h, b, into)
 
     # ------------------------------------------------------------------ feed-forwards
-    def _dense(self, f: DenseFFConfig, lw, h: torch.Tensor) -> torch.Tensor:
-        up = self.linear(h, lw["w_up"], self.act, _lib.EPI_XIELU, lw["act_a"], lw["act_b"])
-        return self.linear(up, lw["w_down"], F32)
+    def _dense(self, f: DenseFFConfig, lw, h: torch.Tensor, into=None) -> torch.Tensor:
+        if f.act == "relu2":
+            up = self.linear(h, lw["w_up"], self.act, _lib.EPI_RELU2)
+        else:
+            up = self.linear(h, lw["w_up"], self.act, _lib.EPI_XIELU, lw["act_a"], lw["act_b"])
+        return self.linear(up, lw["w_down"], F32, into=into)
 
     def _moe(self, f: MoEConfig, lw, h: torch.Tensor) -> torch.Tensor:
         T, D = h.shape
@@ -560,20 +753,27 @@ class SeqLMEngine:
         """embedding -> layers -> (final norm, head) over the rows `want` (a device index tensor, "all", or None)"""
         cfg, D = self.cfg, self.cfg.width
         x = self._empty((b.R, D), F32)
-        rc = self.L.lp_embed_rows_f32(_lib.ptr(b.tokens), b.R, _lib.ptr(self.w.embed), self.w.embed.stride(0), cfg.vocab, _lib.ptr(x),
-                                      x.stride(0), D, self._stream())
+        rc = self.L.lp_embed_rows_f32(_lib.ptr(b.tokens), b.R, _lib.ptr(self.w.embed), self.w.embed.stride(0), cfg.vocab, cfg.embed_scale,
+                                      _lib.ptr(x), x.stride(0), D, self._stream())
         self._check(rc, "lp_embed_rows_f32")
+        pre = cfg.norm == "pre"
         for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
             h = self.norm(x, lw["norm1"], self.act)
-            if isinstance(lc.mixer, RetentionConfig):
-                mixed = self._retention(li, lc.mixer, lw, h, b)
+            if pre:        # x <- x + m * mixer(norm(x)): the update is the store of the mixer's output product
+                self._mix(li, lc.mixer, lw, h, b, into=(x, cfg.residual_mult))
             else:
-                mixed = self._latent(li, lc.mixer, lw, h, b)
-            self.norm(mixed, lw["norm1b"], accum=x)
+                self.norm(self._mix(li, lc.mixer, lw, h, b), lw["norm1b"], accum=x)
             if lc.ff is not None:
                 h = self.norm(x, lw["norm2"], self.act)
-                y = self._dense(lc.ff, lw, h) if isinstance(lc.ff, DenseFFConfig) else self._moe(lc.ff, lw, h)
-                self.norm(y, lw["norm2b"], accum=x)
+                if pre and isinstance(lc.ff, DenseFFConfig):
+                    self._dense(lc.ff, lw, h, into=(x, cfg.residual_mult))
+                elif pre:
+                    y = self._moe(lc.ff, lw, h)
+                    rc = self.L.lp_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0), cfg.residual_mult, b.R, D, self._stream())
+                    self._check(rc, "lp_axpy_f32")
+                else:
+                    y = self._dense(lc.ff, lw, h) if isinstance(lc.ff, DenseFFConfig) else self._moe(lc.ff, lw, h)
+                    self.norm(y, lw["norm2b"], accum=x)
             if self.tap is not None:
                 self.tap(li, x)
         if want is None:
