@@ -13,9 +13,10 @@
 //                         rotated and written: q in place, k and v into the request's page.
 //   lp_window_attn_pool   one CTA per completed block: the mean of its P cached rows -> the block's row in the pooled pool.
 //   lp_window_attn        one CTA per (row, group of QH query heads that share a key / value head).  Keys are walked 32 at a time by
-//                         each warp: every LANE owns one key and computes its QH scores (q in shared memory, the key row read once
-//                         for all QH heads), the warp agrees on the running maximum, then the 32 values are accumulated with the
-//                         lanes spread over vdim (weights broadcast through shared memory).  The CTA's warps take every W-th tile
+//                         each warp: every LANE owns one key and its QH scores (q in shared memory, the key row read once for all
+//                         QH heads; when dim is a multiple of 16 four lanes share the reading of a key, 64 contiguous bytes at a
+//                         time), the warp agrees on the running maximum, then the 32 values are accumulated with the
+//                         lanes spread over vdim (weights and row addresses broadcast through shared memory).  The CTA's warps take every W-th tile
 //                         and merge their (maximum, denominator, sum) triples at the end.  All of it in fp32.
 #include "lp_host.h"
 #include "../../include/leopard_b200.h"
@@ -170,7 +171,8 @@ window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   }
 }
 
-__global__ void __launch_bounds__(128)
+constexpr int WIN_POOL_THREADS = 128;
+__global__ void __launch_bounds__(WIN_POOL_THREADS)
 window_attn_pool_kernel(WinArgs a, int n_seqs, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0) {
   const int s = blockIdx.x;
   if (s >= n_seqs) return;
@@ -178,12 +180,11 @@ window_attn_pool_kernel(WinArgs a, int n_seqs, const int* __restrict__ seq_row0,
   const int b = pos0 / a.pool + blockIdx.y;
   if (b >= (pos0 + len) / a.pool) return;      // block b is complete when its last token b P + P - 1 has been written
   const int roww = a.kv_heads * (a.dim + a.vdim);
-  float* dst = win_block_row(a, s, b);
-  for (int c = threadIdx.x; c < roww; c += blockDim.x) {
-    float sum = 0.f;
-    for (int j = 0; j < a.pool; ++j) sum += win_token_row(a, s, b * a.pool + j)[c];
-    dst[c] = sum / (float)a.pool;
-  }
+  const int c = blockIdx.z * WIN_POOL_THREADS + threadIdx.x;      // one column of the row per thread, the rows in their order
+  if (c >= roww) return;
+  float sum = 0.f;
+  for (int j = 0; j < a.pool; ++j) sum += win_token_row(a, s, b * a.pool + j)[c];
+  win_block_row(a, s, b)[c] = sum / (float)a.pool;
 }
 
 template <int QH, int NV>
@@ -196,7 +197,8 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, W = blockDim.x >> 5;
   const int ratio = a.heads / a.kv_heads, per_g = ratio / QH;
   const int g = blockIdx.y / per_g, h0 = g * ratio + (blockIdx.y % per_g) * QH;
-  float* q_s = dyn_smem;                    // [QH][dim]
+  const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [W][32] cache row of each key of a warp's current tile
+  float* q_s = dyn_smem + 2 * W * 32;       // [QH][dim]
   float* p_s = q_s + QH * a.dim;            // [W][QH][32] softmax weights of a warp's current tile
   float* m_s = p_s + W * QH * 32;           // [W][QH]
   float* d_s = m_s + W * QH;                // [W][QH]
@@ -209,6 +211,7 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
   const WinVisible vis = win_visible(a, pos);
   const int v_off = a.kv_heads * a.dim + g * a.vdim;
   const bool vec = (a.dim % 4 == 0) && (a.vdim % 4 == 0);      // rows and head offsets are then 16-byte aligned
+  const bool quads = vec && (a.dim % 16 == 0);
   float mx[QH], den[QH], acc[QH][NV];
 #pragma unroll
   for (int h = 0; h < QH; ++h) {
@@ -219,24 +222,64 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
     for (int i = 0; i < NV; ++i) acc[h][i] = 0.f;
   }
   float* my_p = p_s + warp * QH * 32;
+  const float** my_row = row_s + warp * 32;
   for (int t0 = warp * 32; t0 < vis.count; t0 += W * 32) {
     const int t = t0 + lane;
     const bool valid = t < vis.count;
     float sc[QH];
 #pragma unroll
     for (int h = 0; h < QH; ++h) sc[h] = 0.f;
-    if (valid) {
-      const float* kp = win_visible_row(a, vis, seq, t) + g * a.dim;
+    if (quads) {
+      // four lanes share a key: each reads every fourth 16-byte piece of the row, so one load instruction of the warp touches 8 rows
+      // of 64 contiguous bytes instead of 32 rows; four passes cover the tile's 32 keys, the partial sums meet by two shuffles
+      const int piece = lane & 3, kq = lane >> 2;
+      for (int i = 0; i < 4; ++i) {
+        const int tk = t0 + i * 8 + kq;
+        float part[QH];
+#pragma unroll
+        for (int h = 0; h < QH; ++h) part[h] = 0.f;
+        if (tk < vis.count) {
+          const float* row = win_visible_row(a, vis, seq, tk);
+          if (piece == 0) my_row[i * 8 + kq] = row;
+          const float* kp = row + g * a.dim + 4 * piece;
+          const float* qp = q_s + 4 * piece;
+          for (int d = 0; d < a.dim; d += 16) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
+#pragma unroll
+            for (int h = 0; h < QH; ++h) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qp + h * a.dim + d);
+              part[h] = fmaf(q4.x, k4.x, part[h]);
+              part[h] = fmaf(q4.y, k4.y, part[h]);
+              part[h] = fmaf(q4.z, k4.z, part[h]);
+              part[h] = fmaf(q4.w, k4.w, part[h]);
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < QH; ++h) {
+          part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
+          part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
+          if (piece == 0) my_p[h * 32 + i * 8 + kq] = part[h];
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < QH; ++h) sc[h] = my_p[h * 32 + lane];      // lane j takes key j's scores
+      __syncwarp();                                                  // all read before the weights overwrite them
+    } else if (valid) {
+      const float* row = win_visible_row(a, vis, seq, t);
+      my_row[lane] = row;      // the value pass finds the row here instead of walking the page table again
+      const float* kp = row + g * a.dim;
       if (vec) {
         for (int d = 0; d < a.dim; d += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
 #pragma unroll
           for (int h = 0; h < QH; ++h) {
-            const float* qh = q_s + h * a.dim + d;
-            sc[h] = fmaf(qh[0], k4.x, sc[h]);
-            sc[h] = fmaf(qh[1], k4.y, sc[h]);
-            sc[h] = fmaf(qh[2], k4.z, sc[h]);
-            sc[h] = fmaf(qh[3], k4.w, sc[h]);
+            const float4 q4 = *reinterpret_cast<const float4*>(q_s + h * a.dim + d);      // one broadcast 16-byte read
+            sc[h] = fmaf(q4.x, k4.x, sc[h]);
+            sc[h] = fmaf(q4.y, k4.y, sc[h]);
+            sc[h] = fmaf(q4.z, k4.z, sc[h]);
+            sc[h] = fmaf(q4.w, k4.w, sc[h]);
           }
         }
       } else {
@@ -270,8 +313,9 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
     }
     __syncwarp();
     const int cnt = vis.count - t0 < 32 ? vis.count - t0 : 32;
+#pragma unroll 4
     for (int jj = 0; jj < cnt; ++jj) {
-      const float* vp = win_visible_row(a, vis, seq, t0 + jj) + v_off;
+      const float* vp = my_row[jj] + v_off;
       float pj[QH];
 #pragma unroll
       for (int h = 0; h < QH; ++h) pj[h] = my_p[h * 32 + jj];
@@ -377,7 +421,7 @@ constexpr int WIN_MAX_DIM = 256;
 constexpr int WIN_SPLIT_ROWS = 16;      // up to this many rows (decoding) a CTA has 8 warps, else 4
 
 static size_t win_smem_floats(int qh, int w, int dim, int vdim) {
-  return (size_t)qh * dim + (size_t)w * qh * 32 + 2 * (size_t)w * qh + (size_t)w * qh * vdim + (size_t)qh * vdim;
+  return 2 * (size_t)w * 32 + (size_t)qh * dim + (size_t)w * qh * 32 + 2 * (size_t)w * qh + (size_t)w * qh * vdim + (size_t)qh * vdim;
 }
 
 template <int QH>
@@ -424,7 +468,9 @@ extern "C" int lp_window_attn_pool(const lp_window_attn_desc* d, int n_seqs, con
   LP_REQUIRE(d->pool > 0 && seq_row0 != nullptr && seq_pos0 != nullptr, "lp_window_attn_pool: no pooled blocks in this description");
   if (n_seqs <= 0 || max_new_blocks <= 0) return 0;
   LP_REQUIRE(max_new_blocks <= 65535, "lp_window_attn_pool: %d blocks per request in one step", max_new_blocks);
-  window_attn_pool_kernel<<<dim3(n_seqs, max_new_blocks), 128, 0, stream>>>(a, n_seqs, seq_row0, seq_pos0);
+  const int roww = d->kv_heads * (d->dim + d->vdim);
+  window_attn_pool_kernel<<<dim3(n_seqs, max_new_blocks, (roww + WIN_POOL_THREADS - 1) / WIN_POOL_THREADS), WIN_POOL_THREADS, 0, stream>>>(
+      a, n_seqs, seq_row0, seq_pos0);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

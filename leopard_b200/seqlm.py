@@ -210,11 +210,11 @@ class SeqLMWeights:
         for i, lc in enumerate(cfg.layers):
             if lc.weights_of is not None:
                 j = lc.weights_of
-                if not 0 <= j < i or cfg.layers[j].weights_of is not None:
-                    raise ValueError(f"layer {i}: weights_of = {j} must name an earlier layer that has tensors of its own")
+                if not 0 <= j < len(cfg.layers) or cfg.layers[j].weights_of is not None:
+                    raise ValueError(f"layer {i}: weights_of = {j} must name a layer that has tensors of its own")
                 if (cfg.layers[j].mixer, cfg.layers[j].ff) != (lc.mixer, lc.ff):
                     raise ValueError(f"layer {i} differs from layer {j}, whose weights it uses")
-                self.layers.append(self.layers[j])
+                self.layers.append(None)              # linked below, once every owner is loaded
                 continue
             lw: Dict[str, object] = {"norm1": one_plus(i, "norm1")} if pre else {k: num(i, k) for k in ("norm1", "norm1b")}
             m = lc.mixer
@@ -282,6 +282,9 @@ class SeqLMWeights:
                     lw["ws_down"] = mat(w(i, "mlp.shared.down", (D, f.shared_ff)))
                     lw["w_sg"] = mat(w(i, "mlp.shared.sg").reshape(D))
             self.layers.append(lw)
+        for i, lc in enumerate(cfg.layers):
+            if lc.weights_of is not None:
+                self.layers[i] = self.layers[lc.weights_of]
 
 
 # ---------------------------------------------------------------------------------------------------------------- batches

@@ -43,9 +43,11 @@ def _prompt_then_decode(eng, toks, n_prompt, key="r"):
 
 LAYERS = {
     "pooled": pooled_layer(),
-    "pooled, odd sizes": pooled_layer(heads=3, kv_heads=3, dim=6, vdim=10, window=4, pool=5, rot_dims=6, factor=None, softcap=None),
+    "pooled, odd sizes": pooled_layer(heads=3, kv_heads=3, dim=6, vdim=10, window=4, pool=3, rot_dims=6, factor=None, softcap=None),
     "pooled, blocks of one": pooled_layer(heads=2, kv_heads=1, dim=4, vdim=4, window=3, pool=1, rot_dims=2),
+    "pooled, heads of sixteen": pooled_layer(heads=4, kv_heads=1, dim=16, vdim=8, window=9, pool=4, rot_dims=8),
     "sink": sink_layer(),
+    "sink, heads of sixteen": sink_layer(heads=2, kv_heads=1, dim=16, vdim=12, window=6, keep_first=2, rot_dims=16),
     "sink, nothing kept": sink_layer(heads=2, kv_heads=2, dim=4, vdim=6, window=6, keep_first=0, rot_dims=2),
     "sink, eight heads a group": sink_layer(heads=8, kv_heads=1, dim=4, vdim=4, window=4, keep_first=5, rot_dims=4),
     "mingru": gru_layer(),
@@ -58,26 +60,27 @@ def test_each_mechanism_alone(backend, name):
     """a one-layer model: the whole prompt in one step, and the same tokens with the last ones decoded through cache and state"""
     cfg = model([LAYERS[name]])
     w = O.random_weights(cfg, seed=3, sharp=2.0)
-    toks = _tokens(19, cfg["vocab"], seed=1)
+    toks = _tokens(14, cfg["vocab"], seed=1)
     res = []
     want = O.forward(cfg, w, toks, residuals=res)
     eng = make_engine(cfg, w, backend)
     taps = []
     eng.tap = lambda li, x: taps.append(x.clone())
-    got = eng.step([StepEntry("p", toks, _all(19))])
+    got = eng.step([StepEntry("p", toks, _all(14))])
     assert rel_err(taps[0], res[0]) < TOL["float32"]              # the residual stream after the layer
     assert float(_rows(got, want).max()) < 5 * TOL["float32"]
     eng.tap = None
     eng.finish("p")
-    assert float(_rows(_prompt_then_decode(eng, toks, 6), want).max()) < 5 * TOL["float32"]
+    assert float(_rows(_prompt_then_decode(eng, toks, 8), want).max()) < 5 * TOL["float32"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompt_then_long_decoding(backend, dtype):
-    """a prompt, then 30 tokens one by one: past both windows, over many page borders, with blocks that complete while decoding"""
+    """a prompt, then 19 tokens one by one (7 in the serving precision): past both windows, over many page borders, with blocks that
+    complete while decoding"""
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=11)
-    toks = _tokens(39, cfg["vocab"], seed=2)
+    toks = _tokens(28 if dtype == "float32" else 16, cfg["vocab"], seed=2)
     want = O.forward(cfg, w, toks)
     eng = make_engine(cfg, w, backend, dtype)
     got = _prompt_then_decode(eng, toks, 9)
@@ -86,7 +89,7 @@ def test_prompt_then_long_decoding(backend, dtype):
         assert float(_rows(got, want).max()) < 5 * TOL[dtype]
 
 
-@pytest.mark.parametrize("cuts", [(2, 2, 3, 9, 2, 6), (7, 17), (1, 2, 21), (12, 12)])
+@pytest.mark.parametrize("cuts", [(2, 2, 3, 9, 2, 4), (7, 15), (1, 2, 19)])
 def test_portions_of_a_prompt(backend, cuts):
     """a prompt fed in portions: blocks that start in one portion and end in another, windows that reach into earlier portions"""
     cfg = mixed_model()
@@ -106,7 +109,7 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     pages, summary pages and slot that were given back (the pools are sized so that it must)"""
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=13)
-    lens = {"a": (1, 3), "b": (11, 7), "c": (18, 2)}            # prompt length, decoded tokens
+    lens = {"a": (1, 3), "b": (11, 4), "c": (14, 2)}            # prompt length, decoded tokens
     toks = {k: _tokens(p + d, cfg["vocab"], seed=30 + i) for i, (k, (p, d)) in enumerate(lens.items())}
     want = {k: O.forward(cfg, w, toks[k]) for k in lens}
     eng = make_engine(cfg, w, backend, max_tokens=8, max_seqs=3)
@@ -115,7 +118,7 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     for i, k in enumerate(lens):
         got[k].append(out[i:i + 1])
     live = list(lens)
-    for step in range(7):
+    for step in range(4):
         live = [k for k in live if step < lens[k][1]]
         out = eng.step([StepEntry(k, [toks[k][lens[k][0] + step]], [0]) for k in live])
         for i, k in enumerate(live):
@@ -128,17 +131,18 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     c = eng.cache
     assert c.pages_in_use() == 0 and len(c.free_slots) == c.n_slots and len(c.summary_free[0]) == c.summary_n_pages[0]
     before = (c.n_slots, c.n_pages, tuple(c.summary_n_pages))
-    t2 = _tokens(17, cfg["vocab"], seed=77)
-    again = eng.step([StepEntry("a", t2, _all(17))])           # the name of an ended request, a used slot, used pages
+    t2 = _tokens(15, cfg["vocab"], seed=77)
+    again = eng.step([StepEntry("a", t2, _all(15))])           # the name of an ended request, a used slot, used pages
     assert float(_rows(again, O.forward(cfg, w, t2)).max()) < 5 * TOL["float32"]
     assert (c.n_slots, c.n_pages, tuple(c.summary_n_pages)) == before
 
 
 def test_pages_given_back_while_running_and_kept_pages_stay(backend):
-    """the window bounds the token pages a request holds, except the pages of the kept first tokens; summary pages stay"""
-    cfg = model([sink_layer(window=5, keep_first=3), pooled_layer(window=6, pool=2)])
+    """the window bounds the token pages a request holds, except the pages of the kept first tokens; summary pages stay; two pooled
+    layers with different block sizes keep two summary page tables"""
+    cfg = model([sink_layer(window=5, keep_first=3), pooled_layer(window=6, pool=2), pooled_layer(heads=2, kv_heads=2, window=4, pool=3)])
     w = O.random_weights(cfg, seed=14, sharp=2.0)
-    toks = _tokens(41, cfg["vocab"], seed=4)
+    toks = _tokens(29, cfg["vocab"], seed=4)
     want = O.forward(cfg, w, toks)
     eng = make_engine(cfg, w, backend, max_tokens=16, max_seqs=1)
     got = [eng.step([StepEntry("r", toks[:6], _all(6))])]
@@ -147,7 +151,8 @@ def test_pages_given_back_while_running_and_kept_pages_stay(backend):
         seq = eng.cache.get("r")
         assert seq.pages[0] >= 0                             # tokens 0..2 live in page 0 for ever
         assert eng.cache.pages_in_use() <= 1 + 3             # one kept page + a window of 6 rows over pages of 4
-    assert len(eng.cache.get("r").summary_pages[0]) == -(-(41 // 2) // 4)
+    assert eng.cache.summary_every == [2, 3]
+    assert [len(p) for p in eng.cache.get("r").summary_pages] == [-(-(29 // 2) // 4), -(-(29 // 3) // 4)]
     assert float(_rows(torch.cat(got, 0), want).max()) < 5 * TOL["float32"]
 
 
@@ -171,31 +176,31 @@ def test_edges_of_what_is_visible(backend, mode, kind):
         layer, wrong = pooled_layer(window=5, pool=3), {"size": 6}
     cfg = model([layer], residual_mult=1.0)
     w = O.random_weights(cfg, seed=15, sharp=4.0)
-    toks = _tokens(26, cfg["vocab"], seed=5)
+    toks = _tokens(20, cfg["vocab"], seed=5)
     want = O.forward(cfg, w, toks)
     off = O.forward(model([_edited(layer, **wrong)], residual_mult=1.0), w, toks)
     assert float(_rows(off, want).max()) > 200 * TOL["float32"]
     eng = make_engine(cfg, w, backend)
-    got = eng.step([StepEntry("r", toks, _all(26))]) if mode == "prompt" else _prompt_then_decode(eng, toks, 3)
+    got = eng.step([StepEntry("r", toks, _all(20))]) if mode == "prompt" else _prompt_then_decode(eng, toks, 3)
     assert float(_rows(got, want).max()) < 5 * TOL["float32"]
 
 
 def test_a_far_key_that_stands_out(backend):
-    """One early token, 60 positions back and 15 pages away, is given a large value row and a key that the late queries look for: it
-    reaches them only through its pooled block (pooled layer) or as a kept first token (sink layer), and it must."""
+    """With large values and sharp scores one early token, 40 positions back and 10 pages away, still shapes the late rows: it reaches
+    them only through its pooled block (pooled layer) or as a kept first token (sink layer), and it must."""
     for layer, at in ((pooled_layer(heads=2, kv_heads=1, window=6, pool=4, softcap=None), 5), (sink_layer(window=6, keep_first=3), 1)):
         cfg = model([layer], vocab=40, residual_mult=1.0)
         w = O.random_weights(cfg, seed=16, sharp=3.0)
         w["l0.mix.v"] = (w["l0.mix.v"].float() * 3).to(torch.bfloat16)
-        toks = _tokens(66, 39, seed=6)
+        toks = _tokens(46, 39, seed=6)
         toks[at] = 39
         quiet = list(toks)
         quiet[at] = 0
         want = O.forward(cfg, w, toks)
-        assert float(_rows(O.forward(cfg, w, quiet)[60:], want[60:]).max()) > 100 * TOL["float32"]    # the far token matters there
-        eng = make_engine(cfg, w, backend, max_tokens=80)
-        got = [eng.step([StepEntry("r", toks[:58], [57])])] + [eng.step([StepEntry("r", [t], [0])]) for t in toks[58:]]
-        assert float(_rows(torch.cat(got, 0), want[57:]).max()) < 5 * TOL["float32"]
+        assert float(_rows(O.forward(cfg, w, quiet)[40:], want[40:]).max()) > 100 * TOL["float32"]    # the far token matters there
+        eng = make_engine(cfg, w, backend, max_tokens=64)
+        got = [eng.step([StepEntry("r", toks[:41], [40])])] + [eng.step([StepEntry("r", [t], [0])]) for t in toks[41:]]
+        assert float(_rows(torch.cat(got, 0), want[40:]).max()) < 5 * TOL["float32"]
 
 
 def test_state_of_the_recurrence_over_chunks_and_slots(backend):
@@ -204,7 +209,7 @@ def test_state_of_the_recurrence_over_chunks_and_slots(backend):
     cfg = model([gru_layer(width=10)], vocab=30, residual_mult=1.0)
     w = O.random_weights(cfg, seed=17)
     w["l0.mix.z.b"] = torch.full((10,), -4.0).to(torch.bfloat16)
-    toks = _tokens(90, 30, seed=7)
+    toks = _tokens(86, 30, seed=7)
     want = O.forward(cfg, w, toks)
     other = list(toks)
     other[2] = (toks[2] + 1) % 30
@@ -212,7 +217,7 @@ def test_state_of_the_recurrence_over_chunks_and_slots(backend):
     eng = make_engine(cfg, w, backend, max_seqs=1)
     got = [eng.step([StepEntry("r", toks[:45], [44])]), eng.step([StepEntry("r", toks[45:80], [34])])]
     got += [eng.step([StepEntry("r", [t], [0])]) for t in toks[80:]]
-    assert float(_rows(torch.cat(got, 0), want[[44] + list(range(79, 90))]).max()) < 5 * TOL["float32"]
+    assert float(_rows(torch.cat(got, 0), want[[44] + list(range(79, 86))]).max()) < 5 * TOL["float32"]
     eng.finish("r")
     t2 = _tokens(5, 30, seed=8)
     assert float(_rows(eng.step([StepEntry("s", t2, _all(5))]), O.forward(cfg, w, t2)).max()) < 5 * TOL["float32"]
@@ -236,9 +241,9 @@ def test_sizes_that_are_equal_or_one(backend, dtype):
 def test_greedy_generation_through_the_scheduler(backend):
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=19)
-    prompts = [_tokens(n, cfg["vocab"], seed=40 + n) for n in (3, 10, 1)]
+    prompts = [_tokens(n, cfg["vocab"], seed=40 + n) for n in (3, 9, 1)]
     eng = make_engine(cfg, w, backend, max_seqs=2)
-    outs = generate(eng, prompts, max_new_tokens=5)
+    outs = generate(eng, prompts, max_new_tokens=3)
     for p, o in zip(prompts, outs):
         seq = list(p)
         for t in o:                                   # every generated token is the oracle's arg-max given what came before
@@ -246,11 +251,11 @@ def test_greedy_generation_through_the_scheduler(backend):
             top2 = lg.topk(2).values
             assert int(lg.argmax()) == t or float(top2[0] - top2[1]) < 1e-3
             seq.append(t)
-        assert len(o) == 5
+        assert len(o) == 3
     assert eng.cache.pages_in_use() == 0
     sched = Scheduler(eng, max_running=1)
     first = outs[0][0]
-    sched.add(Request("x", prompts[0], max_new_tokens=5, eos={first}))
+    sched.add(Request("x", prompts[0], max_new_tokens=3, eos={first}))
     sched.add(Request("y", prompts[1], max_new_tokens=2))
     done = sched.run()
     assert done["x"].output == [first] and done["y"].output == outs[1][:2]
