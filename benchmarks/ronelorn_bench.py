@@ -107,7 +107,8 @@ def bench_ronelorn(name, s, dev, steps, warmup, peaks, prompt):
 
     def per_s(key, amount, unit):
         return round(amount / (kp[key]["ms"] * 1e-3) / unit, 2) if key in kp and kp[key]["ms"] > 0 else None
-    r = {"lp_gemm_bf16_tflops": per_s("lp_gemm_bf16", flops_gemm, 1e12), "lp_window_attn_tflops": per_s("lp_window_attn", attn_flops, 1e12),
+    attn_key = "lp_window_attn_tiles" if "lp_window_attn_tiles" in kp else "lp_window_attn"      # prompts run the row-tile kernel
+    r = {"lp_gemm_bf16_tflops": per_s("lp_gemm_bf16", flops_gemm, 1e12), "lp_window_attn_tflops": per_s(attn_key, attn_flops, 1e12),
          "lp_mingru_prefill_gbs": per_s("lp_mingru_prefill", gru_bytes, 1e9), "lp_window_attn_prep_gbs": per_s("lp_window_attn_prep", prep_bytes, 1e9)}
     r["lp_gemm_bf16_of_bf16_peak"] = round(r["lp_gemm_bf16_tflops"] / peaks["bf16_burst"], 3) if r["lp_gemm_bf16_tflops"] else None
     r["lp_window_attn_of_fp32_fma_peak"] = round(r["lp_window_attn_tflops"] / FP32_FMA_TFLOPS, 3) if r["lp_window_attn_tflops"] else None

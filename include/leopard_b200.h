@@ -689,6 +689,10 @@ int lp_window_attn_pool(const lp_window_attn_desc* desc, int n_seqs, const int* 
 /* out [rows, heads * vdim] fp32 or bf16 */
 int lp_window_attn(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
                    int out_fp32, void* stream);
+/* the same result for the rows of prompts, computed per tile of consecutive rows of one request: the chunk tables of
+ * lp_retention_prefill (at most LP_RETENTION_CHUNK rows a chunk, never across requests) say which rows belong together */
+int lp_window_attn_tiles(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, int n_chunks, const int* chunk_seq,
+                         const int* chunk_row0, const int* chunk_len, void* out, long long ldo, int out_fp32, void* stream);
 
 /* minGRU: z = sigmoid(zxg[:, z_off + c] + z_bias[c]), u = zxg[:, x_off + c] + x_bias[c], candidate = u + 1/2 (u >= 0) or sigmoid(u)
  * (u < 0); S_t = (1 - z) S_(t-1) + z candidate per channel, out = S_t * silu(zxg[:, g_off + c]).  state fp32 [slots][width], carried

@@ -213,6 +213,7 @@ _SIGS = {
     "lp_window_attn_prep": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp]),
     "lp_window_attn_pool": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp]),
     "lp_window_attn": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_window_attn_tiles": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
     "lp_mingru_workspace_bytes": (_sz, [_i, _i]),
     "lp_mingru_prefill": (_i, [C.POINTER(MinGRUDesc), _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "lp_mingru_decode": (_i, [C.POINTER(MinGRUDesc), _i, _vp, _vp, _vp, _vp]),
@@ -271,7 +272,8 @@ STREAM32_LIB_PATH = PKG / "lib" / "libleopard_stream32.so"
 STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_linear", "lp_linear_grouped", "lp_linear_tile_rows", "lp_linear_pairs",
                     "lp_embed_rows_f32", "lp_rmsnorm_f32", "lp_glu_f32", "lp_retention_workspace_bytes", "lp_retention_prefill",
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
-                    "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_mingru_workspace_bytes",
+                    "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_window_attn_tiles",
+                    "lp_mingru_workspace_bytes",
                     "lp_mingru_prefill", "lp_mingru_decode")
 STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None

@@ -18,6 +18,8 @@
 //                         time), the warp agrees on the running maximum, then the 32 values are accumulated with the
 //                         lanes spread over vdim (weights and row addresses broadcast through shared memory).  The CTA's warps take every W-th tile
 //                         and merge their (maximum, denominator, sum) triples at the end.  All of it in fp32.
+//   lp_window_attn_tiles  the same for prompts, a CTA per tile of 2 or 4 consecutive rows of a request: the rows share every key and
+//                         value row the tile reads, each (row, key) pair masked by the row's own rule.
 #include "lp_host.h"
 #include "../../include/leopard_b200.h"
 
@@ -389,6 +391,247 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
   }
 }
 
+// Prompts: one CTA per tile of RQ consecutive rows of one request (a piece of one of the batch's row chunks) and QH query heads of one
+// key / value head, so X = RQ * QH query vectors share every key and value row that is read.  The tile walks the UNION of what its
+// rows see — kept tokens of the last row, blocks of the last row, tokens from the first row's window start to the last row — and
+// every (row, key) pair is masked by the row's own rule, so a row's result is the same as in the one-row kernel up to the order of
+// the sums.  A key can stand in the union twice (as a kept token of a late row and as a window token of an early one); each row
+// sees exactly one of the two.
+template <int QH, int NV, int RQ>
+__global__ void __launch_bounds__(128)
+window_attn_tile_kernel(WinArgs a, int n_chunks, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0,
+                        const int* __restrict__ chunk_len, const int* __restrict__ row_pos, void* __restrict__ out, long long ldo, int out_fp32) {
+  extern __shared__ float dyn_smem[];
+  constexpr int X = RQ * QH;
+  constexpr int TILES = LP_RETENTION_CHUNK / RQ;
+  const int c = blockIdx.x / TILES, sub = blockIdx.x % TILES;
+  if (c >= n_chunks) return;
+  const int len = chunk_len[c];
+  if (sub * RQ >= len) return;
+  const int r0 = chunk_row0[c] + sub * RQ;
+  const int nrows = len - sub * RQ < RQ ? len - sub * RQ : RQ;
+  const int seq = chunk_seq[c], pos0 = row_pos[r0];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, W = blockDim.x >> 5;
+  const int ratio = a.heads / a.kv_heads, per_g = ratio / QH;
+  const int g = blockIdx.y / per_g, h0 = g * ratio + (blockIdx.y % per_g) * QH;
+  const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [W][32]
+  float* q_s = dyn_smem + 2 * W * 32;       // [X][dim]
+  float* p_s = q_s + X * a.dim;             // [W][X][32]
+  float* m_s = p_s + W * X * 32;            // [W][X]
+  float* d_s = m_s + W * X;                 // [W][X]
+  float* o_s = d_s + W * X;                 // [W][X][vdim]
+  float* f_s = o_s + W * X * a.vdim;        // [X][vdim]
+  for (int i = tid; i < X * a.dim; i += blockDim.x) {
+    const int x = i / a.dim, d = i % a.dim, rq = x / QH, h = x % QH;
+    q_s[i] = rq < nrows ? a.qkv[(long long)(r0 + rq) * a.ld + a.q_off + (long long)(h0 + h) * a.dim + d] : 0.f;
+  }
+  __syncthreads();
+  int r_keep[RQ], r_blocks[RQ], r_lo[RQ];
+#pragma unroll
+  for (int rq = 0; rq < RQ; ++rq) {
+    const WinVisible v = win_visible(a, pos0 + (rq < nrows ? rq : nrows - 1));
+    r_keep[rq] = v.n_keep;
+    r_blocks[rq] = v.n_blocks;
+    r_lo[rq] = v.lo;
+  }
+  const WinVisible last = win_visible(a, pos0 + nrows - 1);
+  WinVisible uni;      // the union, in the index space of win_visible_row
+  uni.n_keep = last.n_keep;
+  uni.n_blocks = last.n_blocks;
+  uni.lo = r_lo[0];
+  uni.count = uni.n_keep + uni.n_blocks + (pos0 + nrows - 1 - uni.lo + 1);
+  const int v_off = a.kv_heads * a.dim + g * a.vdim;
+  const bool quads = (a.dim % 16 == 0) && (a.vdim % 4 == 0);
+  float mx[X], den[X], acc[X][NV];
+#pragma unroll
+  for (int x = 0; x < X; ++x) {
+    mx[x] = (a.sink && warp == 0) ? 0.f : -INFINITY;
+    den[x] = (a.sink && warp == 0) ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[x][i] = 0.f;
+  }
+  float* my_p = p_s + warp * X * 32;
+  const float** my_row = row_s + warp * 32;
+  for (int t0 = warp * 32; t0 < uni.count; t0 += W * 32) {
+    const int t = t0 + lane;
+    const bool valid = t < uni.count;
+    float sc[X];
+#pragma unroll
+    for (int x = 0; x < X; ++x) sc[x] = 0.f;
+    if (quads) {
+      // four lanes share a key and every lane works on two keys at a time, so that one 16-byte read of a query serves 8 products
+      const int piece = lane & 3, kq = lane >> 2;
+      for (int i = 0; i < 2; ++i) {
+        const int ka = i * 16 + kq, kb = ka + 8;
+        const bool has_a = t0 + ka < uni.count, has_b = t0 + kb < uni.count;
+        float pa[X], pb[X];
+#pragma unroll
+        for (int x = 0; x < X; ++x) pa[x] = pb[x] = 0.f;
+        if (has_a) {
+          const float* row_a = win_visible_row(a, uni, seq, t0 + ka);
+          const float* row_b = has_b ? win_visible_row(a, uni, seq, t0 + kb) : row_a;
+          if (piece == 0) {
+            my_row[ka] = row_a;
+            my_row[kb] = row_b;
+          }
+          const float* kpa = row_a + g * a.dim + 4 * piece;
+          const float* kpb = row_b + g * a.dim + 4 * piece;
+          const float* qp = q_s + 4 * piece;
+          for (int d = 0; d < a.dim; d += 16) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kpa + d);
+            const float4 l4 = *reinterpret_cast<const float4*>(kpb + d);
+#pragma unroll
+            for (int x = 0; x < X; ++x) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qp + x * a.dim + d);
+              pa[x] = fmaf(q4.x, k4.x, pa[x]);
+              pa[x] = fmaf(q4.y, k4.y, pa[x]);
+              pa[x] = fmaf(q4.z, k4.z, pa[x]);
+              pa[x] = fmaf(q4.w, k4.w, pa[x]);
+              pb[x] = fmaf(q4.x, l4.x, pb[x]);
+              pb[x] = fmaf(q4.y, l4.y, pb[x]);
+              pb[x] = fmaf(q4.z, l4.z, pb[x]);
+              pb[x] = fmaf(q4.w, l4.w, pb[x]);
+            }
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < X; ++x) {
+          pa[x] += __shfl_xor_sync(0xffffffffu, pa[x], 1);
+          pa[x] += __shfl_xor_sync(0xffffffffu, pa[x], 2);
+          pb[x] += __shfl_xor_sync(0xffffffffu, pb[x], 1);
+          pb[x] += __shfl_xor_sync(0xffffffffu, pb[x], 2);
+          if (piece == 0) {
+            my_p[x * 32 + ka] = pa[x];
+            my_p[x * 32 + kb] = pb[x];
+          }
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int x = 0; x < X; ++x) sc[x] = my_p[x * 32 + lane];
+      __syncwarp();
+    } else if (valid) {
+      const float* row = win_visible_row(a, uni, seq, t);
+      my_row[lane] = row;
+      const float* kp = row + g * a.dim;
+      for (int d = 0; d < a.dim; ++d) {
+        const float kv = kp[d];
+#pragma unroll
+        for (int x = 0; x < X; ++x) sc[x] = fmaf(q_s[x * a.dim + d], kv, sc[x]);
+      }
+    }
+    // which of the tile's rows see this lane's key
+    const int seg = t < uni.n_keep ? 0 : (t < uni.n_keep + uni.n_blocks ? 1 : 2);
+    const int idx = seg == 0 ? t : (seg == 1 ? t - uni.n_keep : uni.lo + (t - uni.n_keep - uni.n_blocks));
+#pragma unroll
+    for (int x = 0; x < X; ++x) {
+      const int rq = x / QH;
+      bool seen = valid && rq < nrows;
+      if (seg == 0) seen = seen && idx < r_keep[rq];
+      else if (seg == 1) seen = seen && idx < r_blocks[rq];
+      else seen = seen && idx >= r_lo[rq] && idx <= pos0 + rq;
+      float s = sc[x] * a.scale;
+      if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+      if (!seen) s = -INFINITY;
+      float top = s;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+      const float mn = fmaxf(mx[x], top);
+      const float ref = mn == -INFINITY ? 0.f : mn;      // a row that has seen nothing yet, and sees nothing in this tile
+      const float corr = expf(mx[x] - ref);
+      const float p = seen ? expf(s - ref) : 0.f;
+      float sum = p;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      den[x] = fmaf(den[x], corr, sum);
+      mx[x] = mn;
+      my_p[lane * X + x] = p;      // from here on the buffer holds the weights of a key side by side
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[x][i] *= corr;
+    }
+    __syncwarp();
+    const int cnt = uni.count - t0 < 32 ? uni.count - t0 : 32;
+#pragma unroll 2
+    for (int jj = 0; jj < cnt; ++jj) {
+      const float* vp = my_row[jj] + v_off;
+      float pj[X];
+#pragma unroll
+      for (int x4 = 0; x4 < X / 4; ++x4) {      // X is a multiple of 4: 16-byte broadcast reads
+        const float4 w4 = *reinterpret_cast<const float4*>(my_p + jj * X + 4 * x4);
+        pj[4 * x4] = w4.x;
+        pj[4 * x4 + 1] = w4.y;
+        pj[4 * x4 + 2] = w4.z;
+        pj[4 * x4 + 3] = w4.w;
+      }
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int cc = lane + 32 * i;
+        if (cc < a.vdim) {
+          const float vv = vp[cc];
+#pragma unroll
+          for (int x = 0; x < X; ++x) acc[x][i] = fmaf(pj[x], vv, acc[x][i]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int x = 0; x < X; ++x) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int cc = lane + 32 * i;
+      if (cc < a.vdim) o_s[((long long)warp * X + x) * a.vdim + cc] = acc[x][i];
+    }
+    if (lane == 0) {
+      m_s[warp * X + x] = mx[x];
+      d_s[warp * X + x] = den[x];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < X * a.vdim; i += blockDim.x) {
+    const int x = i / a.vdim, cc = i % a.vdim;
+    float top = -INFINITY;
+    for (int w = 0; w < W; ++w)
+      if (d_s[w * X + x] > 0.f) top = fmaxf(top, m_s[w * X + x]);
+    float total = 0.f, v = 0.f;
+    for (int w = 0; w < W; ++w) {
+      if (d_s[w * X + x] > 0.f) {
+        const float f = expf(m_s[w * X + x] - top);
+        total = fmaf(d_s[w * X + x], f, total);
+        v = fmaf(o_s[((long long)w * X + x) * a.vdim + cc], f, v);
+      }
+    }
+    f_s[i] = total > 0.f ? v / total : 0.f;      // rows past the end of the chunk have seen nothing and are not stored
+  }
+  __syncthreads();
+  const int vhalf = a.v_inv_freq != nullptr ? a.v_rot_dims >> 1 : 0;
+  for (int i = tid; i < X * a.vdim; i += blockDim.x) {
+    const int x = i / a.vdim, cc = i % a.vdim, rq = x / QH, h = x % QH;
+    if (rq >= nrows) continue;
+    const float* o = f_s + x * a.vdim;
+    float v = o[cc];
+    if (cc < 2 * vhalf) {
+      int pair, partner;
+      bool first;
+      if (a.v_rot_layout == LP_ROT_INTERLEAVED) {
+        pair = cc >> 1;
+        first = (cc & 1) == 0;
+        partner = first ? cc + 1 : cc - 1;
+      } else {
+        first = cc < vhalf;
+        pair = first ? cc : cc - vhalf;
+        partner = first ? cc + vhalf : cc - vhalf;
+      }
+      float sn, cs;
+      sincosf((float)(pos0 + rq) * a.v_inv_freq[pair], &sn, &cs);
+      v = first ? o[cc] * cs + o[partner] * sn : o[cc] * cs - o[partner] * sn;
+    }
+    const long long at = (long long)(r0 + rq) * ldo + (long long)(h0 + h) * a.vdim + cc;
+    if (out_fp32) reinterpret_cast<float*>(out)[at] = v;
+    else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16(v);
+  }
+}
+
 static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
   LP_REQUIRE(d != nullptr && d->cache != nullptr && d->page_table != nullptr, "lp_window_attn: null operand");
   LP_REQUIRE(!need_q || d->qkv != nullptr, "lp_window_attn: null projection");
@@ -442,6 +685,29 @@ static int launch_window_attn(const WinArgs& a, int R, const int* row_seq, const
   return 0;
 }
 
+static size_t win_tile_smem_floats(int x, int w, int dim, int vdim) {
+  return 2 * (size_t)w * 32 + (size_t)x * dim + (size_t)w * x * 32 + 2 * (size_t)w * x + (size_t)w * x * vdim + (size_t)x * vdim;
+}
+
+// 0: launched; 1: the sizes do not fit the tile kernel's shared memory (the caller takes the one-row kernel)
+template <int QH, int RQ>
+static int launch_window_attn_tiles(const WinArgs& a, int n_chunks, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
+                                    const int* row_pos, void* out, long long ldo, int out_fp32, cudaStream_t stream) {
+  int warps = 4;
+  while (warps > 1 && win_tile_smem_floats(QH * RQ, warps, a.dim, a.vdim) * sizeof(float) > 48 * 1024) warps >>= 1;
+  const size_t smem = win_tile_smem_floats(QH * RQ, warps, a.dim, a.vdim) * sizeof(float);
+  if (smem > 48 * 1024) return 1;
+  const dim3 grid(n_chunks * (LP_RETENTION_CHUNK / RQ), a.kv_heads * (a.heads / a.kv_heads / QH));
+  const int nv = (a.vdim + 31) / 32;
+  if (nv <= 1) window_attn_tile_kernel<QH, 1, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
+  else if (nv <= 2) window_attn_tile_kernel<QH, 2, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
+  else if (nv <= 4) window_attn_tile_kernel<QH, 4, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
+  else return 1;      // value heads wider than 128 keep too many sums per lane for a tile of rows
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace lp
 
 using namespace lp;
@@ -489,4 +755,24 @@ extern "C" int lp_window_attn(const lp_window_attn_desc* d, int R, const int* ro
   if (ratio % 4 == 0) return launch_window_attn<4>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
   if (ratio % 2 == 0) return launch_window_attn<2>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
   return launch_window_attn<1>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+}
+
+extern "C" int lp_window_attn_tiles(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, int n_chunks,
+                                    const int* chunk_seq, const int* chunk_row0, const int* chunk_len, void* out, long long ldo,
+                                    int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  WinArgs a;
+  if (int rc = fill_win(a, d, true)) return rc;
+  LP_REQUIRE(out != nullptr && row_seq != nullptr && row_pos != nullptr && chunk_seq != nullptr && chunk_row0 != nullptr && chunk_len != nullptr,
+             "lp_window_attn_tiles: null operand");
+  LP_REQUIRE(d->dim <= WIN_MAX_DIM && d->vdim <= WIN_MAX_DIM, "lp_window_attn_tiles: dim=%d / vdim=%d > %d is not instantiated", d->dim,
+             d->vdim, WIN_MAX_DIM);
+  if (R <= 0 || n_chunks <= 0) return 0;
+  const int ratio = d->heads / d->kv_heads;
+  int rc;
+  if (ratio % 4 == 0) rc = launch_window_attn_tiles<4, 2>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  else if (ratio % 2 == 0) rc = launch_window_attn_tiles<2, 4>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  else rc = launch_window_attn_tiles<1, 4>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  if (rc == 1) return lp_window_attn(d, R, row_seq, row_pos, out, ldo, out_fp32, stream_);
+  return rc;
 }

@@ -589,7 +589,12 @@ class SeqLMEngine:
             rc = self.L.lp_window_attn_pool(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), new, st)
             self._check(rc, "lp_window_attn_pool")
         o = self._empty((b.R, m.heads * m.vdim), self.act)
-        rc = self.L.lp_window_attn(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0), int(o.dtype == F32), st)
+        if b.decode:
+            rc = self.L.lp_window_attn(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0),
+                                       int(o.dtype == F32), st)
+        else:      # prompts and portions: tiles of consecutive rows share the keys they read
+            rc = self.L.lp_window_attn_tiles(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), b.n_chunks, _lib.ptr(b.chunk_seq),
+                                             _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len), _lib.ptr(o), o.stride(0), int(o.dtype == F32), st)
         self._check(rc, "lp_window_attn")
         return self.linear(o, lw["w_o"], F32, into=into)
 

@@ -1,5 +1,5 @@
-"""Plain, slow float64 implementation of the Ronelorn layers — the checker of the window-attention, minGRU and pre-norm paths of
-leopard_b200/seqlm.py.  One function per mechanism, whole sequences from position 0 only, explicit loops over queries and keys,
+"""Plain, slow float64 implementation of the Ronelorn layers: what the tests compare the window-attention, minGRU and pre-norm paths
+of leopard_b200/seqlm.py with.  One function per mechanism, whole sequences from position 0 only, explicit loops over queries and keys,
 nothing shared with the product path: it takes the parsed config.json and a {name: tensor} dict.
 
 Notation: T tokens, H query heads, G key / value heads (query head h reads group h // (H // G)), d key size, e value size.
