@@ -400,11 +400,11 @@ window_attn_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int*
 template <int QH, int NV, int RQ>
 __global__ void __launch_bounds__(128)
 window_attn_tile_kernel(WinArgs a, int n_chunks, const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0,
-                        const int* __restrict__ chunk_len, const int* __restrict__ row_pos, void* __restrict__ out, long long ldo, int out_fp32) {
+                        const int* __restrict__ chunk_len, int tiles_per_chunk, const int* __restrict__ row_pos, void* __restrict__ out,
+                        long long ldo, int out_fp32) {
   extern __shared__ float dyn_smem[];
   constexpr int X = RQ * QH;
-  constexpr int TILES = LP_RETENTION_CHUNK / RQ;
-  const int c = blockIdx.x / TILES, sub = blockIdx.x % TILES;
+  const int c = blockIdx.x / tiles_per_chunk, sub = blockIdx.x % tiles_per_chunk;
   if (c >= n_chunks) return;
   const int len = chunk_len[c];
   if (sub * RQ >= len) return;
@@ -691,17 +691,19 @@ static size_t win_tile_smem_floats(int x, int w, int dim, int vdim) {
 
 // 0: launched; 1: the sizes do not fit the tile kernel's shared memory (the caller takes the one-row kernel)
 template <int QH, int RQ>
-static int launch_window_attn_tiles(const WinArgs& a, int n_chunks, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
+static int launch_window_attn_tiles(const WinArgs& a, int R, int n_chunks, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
                                     const int* row_pos, void* out, long long ldo, int out_fp32, cudaStream_t stream) {
   int warps = 4;
   while (warps > 1 && win_tile_smem_floats(QH * RQ, warps, a.dim, a.vdim) * sizeof(float) > 48 * 1024) warps >>= 1;
   const size_t smem = win_tile_smem_floats(QH * RQ, warps, a.dim, a.vdim) * sizeof(float);
   if (smem > 48 * 1024) return 1;
-  const dim3 grid(n_chunks * (LP_RETENTION_CHUNK / RQ), a.kv_heads * (a.heads / a.kv_heads / QH));
+  const int longest = R < LP_RETENTION_CHUNK ? R : LP_RETENTION_CHUNK;      // no chunk has more rows than the step or the chunk size
+  const int tiles = (longest + RQ - 1) / RQ;
+  const dim3 grid(n_chunks * tiles, a.kv_heads * (a.heads / a.kv_heads / QH));
   const int nv = (a.vdim + 31) / 32;
-  if (nv <= 1) window_attn_tile_kernel<QH, 1, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
-  else if (nv <= 2) window_attn_tile_kernel<QH, 2, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
-  else if (nv <= 4) window_attn_tile_kernel<QH, 4, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32);
+  if (nv <= 1) window_attn_tile_kernel<QH, 1, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, tiles, row_pos, out, ldo, out_fp32);
+  else if (nv <= 2) window_attn_tile_kernel<QH, 2, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, tiles, row_pos, out, ldo, out_fp32);
+  else if (nv <= 4) window_attn_tile_kernel<QH, 4, RQ><<<grid, warps * 32, smem, stream>>>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, tiles, row_pos, out, ldo, out_fp32);
   else return 1;      // value heads wider than 128 keep too many sums per lane for a tile of rows
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
@@ -770,9 +772,9 @@ extern "C" int lp_window_attn_tiles(const lp_window_attn_desc* d, int R, const i
   if (R <= 0 || n_chunks <= 0) return 0;
   const int ratio = d->heads / d->kv_heads;
   int rc;
-  if (ratio % 4 == 0) rc = launch_window_attn_tiles<4, 2>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
-  else if (ratio % 2 == 0) rc = launch_window_attn_tiles<2, 4>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
-  else rc = launch_window_attn_tiles<1, 4>(a, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  if (ratio % 4 == 0) rc = launch_window_attn_tiles<4, 2>(a, R, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  else if (ratio % 2 == 0) rc = launch_window_attn_tiles<2, 4>(a, R, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
+  else rc = launch_window_attn_tiles<1, 4>(a, R, n_chunks, chunk_seq, chunk_row0, chunk_len, row_pos, out, ldo, out_fp32, stream);
   if (rc == 1) return lp_window_attn(d, R, row_seq, row_pos, out, ldo, out_fp32, stream_);
   return rc;
 }

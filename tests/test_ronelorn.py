@@ -76,11 +76,11 @@ def test_each_mechanism_alone(backend, name):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompt_then_long_decoding(backend, dtype):
-    """a prompt, then 19 tokens one by one (7 in the serving precision): past both windows, over many page borders, with blocks that
+    """a prompt, then 15 tokens one by one (7 in the serving precision): past both windows, over many page borders, with blocks that
     complete while decoding"""
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=11)
-    toks = _tokens(28 if dtype == "float32" else 16, cfg["vocab"], seed=2)
+    toks = _tokens(24 if dtype == "float32" else 16, cfg["vocab"], seed=2)
     want = O.forward(cfg, w, toks)
     eng = make_engine(cfg, w, backend, dtype)
     got = _prompt_then_decode(eng, toks, 9)
@@ -142,7 +142,7 @@ def test_pages_given_back_while_running_and_kept_pages_stay(backend):
     layers with different block sizes keep two summary page tables"""
     cfg = model([sink_layer(window=5, keep_first=3), pooled_layer(window=6, pool=2), pooled_layer(heads=2, kv_heads=2, window=4, pool=3)])
     w = O.random_weights(cfg, seed=14, sharp=2.0)
-    toks = _tokens(29, cfg["vocab"], seed=4)
+    toks = _tokens(25, cfg["vocab"], seed=4)
     want = O.forward(cfg, w, toks)
     eng = make_engine(cfg, w, backend, max_tokens=16, max_seqs=1)
     got = [eng.step([StepEntry("r", toks[:6], _all(6))])]
@@ -152,7 +152,7 @@ def test_pages_given_back_while_running_and_kept_pages_stay(backend):
         assert seq.pages[0] >= 0                             # tokens 0..2 live in page 0 for ever
         assert eng.cache.pages_in_use() <= 1 + 3             # one kept page + a window of 6 rows over pages of 4
     assert eng.cache.summary_every == [2, 3]
-    assert [len(p) for p in eng.cache.get("r").summary_pages] == [-(-(29 // 2) // 4), -(-(29 // 3) // 4)]
+    assert [len(p) for p in eng.cache.get("r").summary_pages] == [-(-(25 // 2) // 4), -(-(25 // 3) // 4)]
     assert float(_rows(torch.cat(got, 0), want).max()) < 5 * TOL["float32"]
 
 
